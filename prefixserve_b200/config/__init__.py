@@ -1,5 +1,6 @@
 from .llama import Llama3RopeScaling, LlamaConfig, UnsupportedModelError
 from .gekopel import BiasedAttentionConfig, DeltaConfig, DenseFF, GekopelConfig, GekopelLayer, RoutedFF
+from .goganex import AttentionConfig, ClippedFF, GoganexConfig, GoganexLayer, ParallelConfig, RotationConfig
 from .nerenex import LatentAttentionConfig, NerenexConfig, NerenexLayer, RecurrentConfig
 from .registry import (
     Architecture,
@@ -13,7 +14,7 @@ from .registry import (
 from .spec import LayerCall, LayerSpec, ModelSpec, PartSpec, part, sequential_schedule
 
 __all__ = [
-    "Architecture", "BiasedAttentionConfig", "DeltaConfig", "DenseFF", "GekopelConfig", "GekopelLayer", "RoutedFF", "LatentAttentionConfig", "LayerCall", "LayerSpec", "Llama3RopeScaling", "LlamaConfig", "ModelSpec",
+    "Architecture", "AttentionConfig", "ClippedFF", "GoganexConfig", "GoganexLayer", "ParallelConfig", "RotationConfig", "BiasedAttentionConfig", "DeltaConfig", "DenseFF", "GekopelConfig", "GekopelLayer", "RoutedFF", "LatentAttentionConfig", "LayerCall", "LayerSpec", "Llama3RopeScaling", "LlamaConfig", "ModelSpec",
     "NerenexConfig", "NerenexLayer", "PartSpec", "RecurrentConfig",
     "UnknownArchitectureError", "UnsupportedModelError", "architecture_of", "get_architecture", "part",
     "read_model_folder", "register_architecture", "registered_architectures", "sequential_schedule",

@@ -23,7 +23,8 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const TT* __re
   for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = to_float<TT>(row[j]);
 }
 
-// h[t] = table[ids[t]] * scale + pos_table[positions[t]]: token rows times a constant plus learned position rows.
+// h[t] = table[ids[t]] * scale + pos_table[positions[t]]: token rows times a constant plus learned position rows
+// (``pos_table`` null: token rows times the constant only).
 template <typename TT>
 __global__ void embedding_pos_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ positions,
                                      const TT* __restrict__ table, const TT* __restrict__ pos_table, float* __restrict__ out,
@@ -31,12 +32,17 @@ __global__ void embedding_pos_kernel(const int32_t* __restrict__ ids, const int3
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
-  int id = ids[t], p = positions[t];
+  int id = ids[t];
   id = id < 0 ? 0 : (id >= V ? V - 1 : id);
-  p = p < 0 ? 0 : (p >= P ? P - 1 : p);  // positions are checked against the table on the host
   const TT* row = table + (size_t)id * H;
-  const TT* prow = pos_table + (size_t)p * H;
   float* o = out + (size_t)t * H;
+  if (!pos_table) {
+    for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = to_float<TT>(row[j]) * scale;
+    return;
+  }
+  int p = positions[t];
+  p = p < 0 ? 0 : (p >= P ? P - 1 : p);  // positions are checked against the table on the host
+  const TT* prow = pos_table + (size_t)p * H;
   for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = fmaf(to_float<TT>(row[j]), scale, to_float<TT>(prow[j]));
 }
 
@@ -275,6 +281,74 @@ PSB_API int psb_silu_mul(const void* gate_up, int dtype, void* out, int T, int I
   PSB_REFUSE("act_mul: activation code %d is not built", activation);
 }
 
+// The gated feed-forward's activation with both branches clipped: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + offset).  [T, 2I] -> [T, I]; the arithmetic is float32.
+__device__ __forceinline__ float clipped_glu(float g, float u, float limit, float alpha, float offset) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.f + expf(-alpha * g)) * (u + offset);
+}
+
+template <typename T>
+__global__ void clipped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, float limit, float alpha,
+                                   float offset) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / (size_t)I;
+    const int j = (int)(idx - t * (size_t)I);
+    out[idx] = from_float<T>(clipped_glu(to_float<T>(gu[t * 2 * (size_t)I + j]), to_float<T>(gu[t * 2 * (size_t)I + I + j]), limit,
+                                         alpha, offset));
+  }
+}
+
+// Eight elements per thread (16-byte loads and stores).  Needs I % 8 == 0 and bfloat16.
+__global__ void clipped_glu_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I, size_t vecs,
+                                       float limit, float alpha, float offset) {
+  pdl_trigger();
+  pdl_wait();
+  const int per_row = I >> 3;
+  for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < vecs; v += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = v / per_row;
+    const int j = (int)(v - t * per_row) << 3;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * (size_t)I + j);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * (size_t)I + I + j);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+      o2[k] = __floats2bfloat162_rn(clipped_glu(g.x, u.x, limit, alpha, offset), clipped_glu(g.y, u.y, limit, alpha, offset));
+    }
+    *reinterpret_cast<uint4*>(out + t * (size_t)I + j) = o4;
+  }
+}
+
+// (gate_up, dtype, out, T, I, limit, alpha, offset, stream)
+PSB_API int psb_clipped_glu(const void* gate_up, int dtype, void* out, int T, int I, float limit, float alpha, float offset,
+                            cudaStream_t stream) {
+  if (T < 0 || I < 1 || !(limit > 0.f)) PSB_REFUSE("clipped_glu: bad sizes T=%d I=%d or limit %g", T, I, (double)limit);
+  if (T == 0) return 0;
+  if (dtype == PSB_BF16 && I % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+    const size_t vecs = (size_t)T * (I / 8);
+    const size_t want = (vecs + 255) / 256;
+    psb_launch(clipped_glu_vec_kernel, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(256), 0, stream,
+               (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, vecs, limit, alpha, offset);
+    PSB_LAUNCH_CHECK("clipped_glu");
+    return 0;
+  }
+  const size_t total = (size_t)T * I;
+  const size_t want = (total + 255) / 256;
+  PSB_DISPATCH_DTYPE(dtype, T_, {
+    psb_launch(clipped_glu_kernel<T_>, dim3((unsigned)(want < 148 * 32 ? want : 148 * 32)), dim3(256), 0, stream, (const T_*)gate_up,
+               (T_*)out, I, total, limit, alpha, offset);
+  });
+  PSB_LAUNCH_CHECK("clipped_glu");
+  return 0;
+}
+
 // h[T, H] (float32) += delta[T, H]: the residual sum on its own, for block arrangements in which no norm follows it.
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t total) {
@@ -299,7 +373,7 @@ PSB_API int psb_residual_add(void* h, const void* delta, int delta_dtype, long l
 // (ids, positions, table, pos_table, table_dtype, out_f32, T, H, V, P, scale, stream)
 PSB_API int psb_embedding_pos(const void* ids, const void* positions, const void* table, const void* pos_table, int table_dtype,
                               void* out, int T, int H, int V, int P, float scale, cudaStream_t stream) {
-  if (T < 0 || H < 1 || V < 1 || P < 1) PSB_REFUSE("embedding_pos: bad sizes T=%d H=%d V=%d P=%d", T, H, V, P);
+  if (T < 0 || H < 1 || V < 1 || (pos_table && (P < 1 || !positions))) PSB_REFUSE("embedding_pos: bad sizes T=%d H=%d V=%d P=%d", T, H, V, P);
   if (T == 0) return 0;
   PSB_DISPATCH_DTYPE(table_dtype, TT, {
     psb_launch(embedding_pos_kernel<TT>, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream, (const int32_t*)ids,

@@ -1,0 +1,106 @@
+// Token shift: what a sublayer reads is moved toward what it read one token earlier, channel by channel,
+//
+//   y_t = x_t + (x_(t-1) - x_t) * mix        x_(-1) = 0
+//
+// with x_(t-1) the unshifted row of the token before.  For the first token of a portion that row is not in the step:
+// it is carried per request in the slot's state (float32, ``state`` + slot * stride), which the same launch brings up
+// to date with the portion's last row.  One block per token; the block of a portion's first token reads the carried
+// row and then, thread by thread for the same channels, writes the new one, so nobody reads what has been replaced.
+// The interpolation is float32; rows are float32 or bfloat16.
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+token_shift_kernel(const T* __restrict__ x, const float* __restrict__ mix, float* __restrict__ state, long long stride,
+                   const int32_t* __restrict__ positions, const int32_t* __restrict__ token_item,
+                   const int32_t* __restrict__ item_start, const int32_t* __restrict__ slots, T* __restrict__ y, int W,
+                   int num_slots) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int item = token_item[t];
+  const int first = item_start[item], last = item_start[item + 1] - 1;
+  const T* row = x + (size_t)t * W;
+  T* out = y + (size_t)t * W;
+  if (t != first) {
+    const T* before = row - W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      const float a = to_float<T>(row[c]), b = to_float<T>(before[c]);
+      out[c] = from_float<T>(fmaf(b - a, mix[c], a));
+    }
+    return;
+  }
+  const int slot = slots[item];
+  if (slot < 0 || slot >= num_slots) return;  // slots are checked on the host; never touch memory outside the states
+  float* held = state + (size_t)slot * stride;
+  const bool starts = positions[t] == 0;
+  const T* newest = x + (size_t)last * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float a = to_float<T>(row[c]);
+    const float b = starts ? 0.f : held[c];
+    out[c] = from_float<T>(fmaf(b - a, mix[c], a));
+    held[c] = to_float<T>(newest[c]);
+  }
+}
+
+// out = (gain_a * a / rms(a) + gain_b * b / rms(b)) * weight: two branches that read the same input, each normed over
+// the row before they are added.  One block per row, statistics float32, float32 result.
+template <typename T>
+__global__ void __launch_bounds__(256)
+normed_pair_sum_kernel(const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ gain_a,
+                       const float* __restrict__ gain_b, float* __restrict__ out, int W, float eps, float weight) {
+  __shared__ float sums[2][8];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const T* ra = a + (size_t)t * W;
+  const T* rb = b + (size_t)t * W;
+  float sa = 0.f, sb = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float va = to_float<T>(ra[c]), vb = to_float<T>(rb[c]);
+    sa = fmaf(va, va, sa);
+    sb = fmaf(vb, vb, sb);
+  }
+  sa = warp_sum(sa);
+  sb = warp_sum(sb);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sums[0][warp] = sa; sums[1][warp] = sb; }
+  __syncthreads();
+  sa = sb = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { sa += sums[0][w]; sb += sums[1][w]; }
+  const float ia = 1.f / sqrtf(sa / (float)W + eps), ib = 1.f / sqrtf(sb / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x)
+    out[(size_t)t * W + c] = (gain_a[c] * (to_float<T>(ra[c]) * ia) + gain_b[c] * (to_float<T>(rb[c]) * ib)) * weight;
+}
+
+}  // namespace
+
+// (x, dtype, mix, state, stride, positions, token_item, item_start, slots, y, T, W, num_slots, stream)
+PSB_API int psb_token_shift(const void* x, int dtype, const void* mix, void* state, long long stride, const void* positions,
+                            const void* token_item, const void* item_start, const void* slots, void* y, int T, int W,
+                            int num_slots, cudaStream_t stream) {
+  if (T < 0 || W < 1 || num_slots < 1 || stride < W) PSB_REFUSE("token_shift: bad sizes T=%d W=%d stride=%lld", T, W, stride);
+  if (T == 0) return 0;
+  PSB_DISPATCH_DTYPE(dtype, T_, {
+    psb_launch(token_shift_kernel<T_>, dim3(T), dim3(W >= 1024 ? 256 : 128), 0, stream, (const T_*)x, (const float*)mix,
+               (float*)state, stride, (const int32_t*)positions, (const int32_t*)token_item, (const int32_t*)item_start,
+               (const int32_t*)slots, (T_*)y, W, num_slots);
+  });
+  PSB_LAUNCH_CHECK("token_shift");
+  return 0;
+}
+
+// (a, b, dtype, gain_a, gain_b, out_f32, T, W, eps, weight, stream)
+PSB_API int psb_normed_pair_sum(const void* a, const void* b, int dtype, const void* gain_a, const void* gain_b, void* out,
+                                int T, int W, float eps, float weight, cudaStream_t stream) {
+  if (T < 0 || W < 1) PSB_REFUSE("normed_pair_sum: bad sizes T=%d W=%d", T, W);
+  if (T == 0) return 0;
+  PSB_DISPATCH_DTYPE(dtype, T_, {
+    psb_launch(normed_pair_sum_kernel<T_>, dim3(T), dim3(W >= 1024 ? 256 : 128), 0, stream, (const T_*)a, (const T_*)b,
+               (const float*)gain_a, (const float*)gain_b, (float*)out, W, eps, weight);
+  });
+  PSB_LAUNCH_CHECK("normed_pair_sum");
+  return 0;
+}

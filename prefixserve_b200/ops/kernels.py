@@ -46,13 +46,17 @@ def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """h[t] = float32(table[ids[t]])."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor:
+    """h[t] = float32(table[ids[t]]) * scale (the product in float32)."""
     _i32(ids, "token ids")
     _dev(table, "embedding table")
     t, (v, h) = ids.numel(), table.shape
     if out is None:
         out = torch.empty((t, h), dtype=torch.float32, device=ids.device)
+    if scale != 1.0:
+        check(lib().psb_embedding_pos(ids.data_ptr(), None, table.data_ptr(), None, _code(table, "embedding table"), out.data_ptr(),
+                                      t, h, v, 0, float(scale), _stream()), "embedding_pos")
+        return out
     check(lib().psb_embedding(ids.data_ptr(), table.data_ptr(), _code(table, "embedding table"), out.data_ptr(),
                               t, h, v, _stream()), "embedding")
     return out
@@ -771,6 +775,29 @@ def biased_attention(qkv: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, c
         raise KernelError(f"projection output must be [T, {want}], is {tuple(qkv.shape)}")
     if kv.dim() != 5 or tuple(kv.shape[1:]) != (1, num_kv_heads, page_size, dim + vdim):
         raise KernelError(f"cache entry must be [pages, 1, {num_kv_heads}, {page_size}, {dim + vdim}], is {tuple(kv.shape)}")
+    q = torch.empty((t, num_heads, dim), dtype=qkv.dtype, device=qkv.device)
+    check(lib().psb_attention_biased_append(qkv.data_ptr(), _code(qkv, "projection output"), positions.data_ptr(),
+                                            token_item.data_ptr(), table.data_ptr(), table.shape[1], kv.data_ptr(),
+                                            _code(kv, "cache entry"), q.data_ptr(), t, num_heads, num_kv_heads, dim, vdim,
+                                            page_size, kv.shape[0], _stream()), "attention_biased_append")
+    return attention_over_rows(q, kv, table, ctx, num_heads=num_heads, num_kv_heads=num_kv_heads, dim=dim, vdim=vdim,
+                               page_size=page_size, scale=scale, window=window, chunk=chunk, bias=bias, sink=sink)
+
+
+def attention_over_rows(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,
+                        dim: int, vdim: int, page_size: int, scale: float, window: int | None = None, chunk: int | None = None,
+                        bias: torch.Tensor | None = None, sink: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of queries [T, hq, dim] over a cache entry that holds one row per token and key/value head, the
+    key and then the value ([pages, 1, hkv, page_size, dim + vdim]; the step's own rows already appended), with an
+    optional window, chunk mask, distance bias (float32 [heads, reach]) and sink (float32 [heads]: a score per head
+    that joins the softmax denominator without a value) -> [T, hq * vdim]."""
+    _dev(q, "queries"), _dev(kv, "cache entry"), _i32(table, "page table")
+    positions, token_item = _i32(ctx.positions, "positions"), _i32(ctx.token_item, "token-to-item map")
+    t = q.shape[0]
+    if q.dim() != 3 or tuple(q.shape[1:]) != (num_heads, dim):
+        raise KernelError(f"queries must be [T, {num_heads}, {dim}], are {tuple(q.shape)}")
+    if kv.dim() != 5 or tuple(kv.shape[1:]) != (1, num_kv_heads, page_size, dim + vdim):
+        raise KernelError(f"cache entry must be [pages, 1, {num_kv_heads}, {page_size}, {dim + vdim}], is {tuple(kv.shape)}")
     reach = 0
     if bias is not None:
         if bias.dtype != torch.float32 or bias.dim() != 2 or bias.shape[0] != num_heads or not bias.is_cuda or not bias.is_contiguous():
@@ -778,18 +805,13 @@ def biased_attention(qkv: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, c
         reach = bias.shape[1]
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != num_heads or not sink.is_cuda):
         raise KernelError(f"sinks must be float32 [{num_heads}] on the device")
-    q = torch.empty((t, num_heads, dim), dtype=qkv.dtype, device=qkv.device)
-    check(lib().psb_attention_biased_append(qkv.data_ptr(), _code(qkv, "projection output"), positions.data_ptr(),
-                                            token_item.data_ptr(), table.data_ptr(), table.shape[1], kv.data_ptr(),
-                                            _code(kv, "cache entry"), q.data_ptr(), t, num_heads, num_kv_heads, dim, vdim,
-                                            page_size, kv.shape[0], _stream()), "attention_biased_append")
-    out = torch.empty((t, num_heads * vdim), dtype=qkv.dtype, device=qkv.device)
+    out = torch.empty((t, num_heads * vdim), dtype=q.dtype, device=q.device)
     win, chk = int(window or 0), int(chunk or 0)
     # Portions of a bfloat16 step go tile by tile; what is left (single tokens, short portions) walks its keys.  Which
     # kernel a token gets depends on the length of its portion only (decided on the device from the item offsets, so
     # the launches have the same shape whatever the step holds).
     item_start = _i32(ctx.item_start, "item offsets")
-    both16 = qkv.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16
+    both16 = q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16
     on_tensor_cores = both16 and BIASED_MMA and bool(lib().psb_attention_biased_mma_supported(num_heads, num_kv_heads, dim, vdim))
     least = BIASED_MMA_MIN_TOKENS if on_tensor_cores else BIASED_TILE_MIN_TOKENS
     long_portions = both16 and ctx.max_new_tokens >= least
@@ -934,4 +956,126 @@ def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, w_u
                                 _code(shared, "shared expert output") if shared is not None else F32,
                                 _ptr(shared_gate) if shared is not None else None, ldg, out.data_ptr(), _code(out, "experts' sum"),
                                 t, h, top, _stream()), "moe_combine")
+    return out
+
+
+def _f32_vector(x: torch.Tensor, n: int, what: str) -> torch.Tensor:
+    if x.dtype != torch.float32 or x.numel() != n or not x.is_cuda or not x.is_contiguous():
+        raise KernelError(f"{what} must be float32 with {n} numbers on the device, is {x.dtype} {tuple(x.shape)} on {x.device}")
+    return x
+
+
+def _slot_rows(state: torch.Tensor, width: int, what: str) -> int:
+    """A per-slot float32 state [num_slots, >= width] whose rows may be part of wider ones; returns the row stride."""
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != width or not state.is_cuda or state.stride(1) != 1:
+        raise KernelError(f"{what} must be float32 [slots, {width}] on the device with unit stride along a row, is "
+                          f"{state.dtype} {tuple(state.shape)} strides {state.stride()}")
+    return int(state.stride(0))
+
+
+def token_shift(x: torch.Tensor, mix: torch.Tensor, state: torch.Tensor, ctx) -> torch.Tensor:
+    """y_t = x_t + (x_(t-1) - x_t) * mix per channel, with x_(t-1) the row before (zero in front of a sequence's first
+    token); the row before a portion's first token comes from ``state`` [num_slots, W] (float32; rows may be strided),
+    which receives the portion's last row."""
+    _dev(x, "shifted rows")
+    t, w = x.shape
+    stride = _slot_rows(state, w, "token-shift state")
+    _f32_vector(mix, w, "token-shift weights")
+    y = torch.empty_like(x)
+    check(lib().psb_token_shift(x.data_ptr(), _code(x, "shifted rows"), mix.data_ptr(), state.data_ptr(), stride,
+                                _i32(ctx.positions, "positions").data_ptr(), _i32(ctx.token_item, "token-to-item map").data_ptr(),
+                                _i32(ctx.item_start, "item offsets").data_ptr(), _i32(ctx.slots, "slots").data_ptr(), y.data_ptr(),
+                                t, w, state.shape[0], _stream()), "token_shift")
+    return y
+
+
+def normed_pair_sum(a: torch.Tensor, b: torch.Tensor, gain_a: torch.Tensor, gain_b: torch.Tensor, eps: float,
+                    weight: float = 1.0) -> torch.Tensor:
+    """(gain_a * rmsnorm(a) + gain_b * rmsnorm(b)) * weight, row by row, as float32 [T, W]."""
+    _dev(a, "left result"), _dev(b, "right result")
+    if isinstance(a, PendingProduct) or a.dim() != 2 or a.shape != b.shape or a.dtype != b.dtype:
+        raise KernelError(f"the two results must have one shape and type: {a.dtype} {tuple(a.shape)} vs {b.dtype} {tuple(b.shape)}")
+    t, w = a.shape
+    _f32_vector(gain_a, w, "left gain"), _f32_vector(gain_b, w, "right gain")
+    out = torch.empty((t, w), dtype=torch.float32, device=a.device)
+    check(lib().psb_normed_pair_sum(a.data_ptr(), b.data_ptr(), _code(a, "left result"), gain_a.data_ptr(), gain_b.data_ptr(),
+                                    out.data_ptr(), t, w, float(eps), float(weight), _stream()), "normed_pair_sum")
+    return out
+
+
+def attention_prepare(proj: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,
+                      dim: int, vdim: int, page_size: int, cos: torch.Tensor | None = None, sin: torch.Tensor | None = None,
+                      rotary_dim: int | None = None, interleaved: bool = False, unit_norm_eps: float | None = None,
+                      head_factor: torch.Tensor | None = None, values_are_keys: bool = False) -> torch.Tensor:
+    """One pass over the fused projection [T, q | k | v] (or [T, q | k] with ``values_are_keys``): optional rotation of
+    the first ``rotary_dim`` elements of query and key heads by position (``cos``/``sin`` float32 [positions,
+    rotary_dim/2]), optional division of every query and key head by its root mean square (``unit_norm_eps``), an
+    optional float32 factor per query head; keys and values appended to the cache entry [pages, 1, hkv, page_size,
+    dim + vdim].  Returns the queries [T, hq, dim]."""
+    _dev(kv, "cache entry"), _i32(table, "page table")
+    t = proj.shape[0]
+    want = num_heads * dim + num_kv_heads * dim + (0 if values_are_keys else num_kv_heads * vdim)
+    if not proj.is_cuda or proj.dim() != 2 or proj.shape[1] != want or proj.stride(1) != 1:
+        raise KernelError(f"projection output must be [T, {want}] on the device (rows may be part of wider ones), is {tuple(proj.shape)}")
+    if kv.dim() != 5 or tuple(kv.shape[1:]) != (1, num_kv_heads, page_size, dim + vdim):
+        raise KernelError(f"cache entry must be [pages, 1, {num_kv_heads}, {page_size}, {dim + vdim}], is {tuple(kv.shape)}")
+    if values_are_keys and vdim != dim:
+        raise KernelError(f"keys that serve as values need vdim == dim, not {vdim} and {dim}")
+    max_pos = 0
+    rotary_dim = dim if rotary_dim is None else int(rotary_dim)
+    if cos is not None:
+        if sin is None or cos.shape != sin.shape or cos.dtype != torch.float32 or cos.dim() != 2 or cos.shape[1] != rotary_dim // 2 \
+                or rotary_dim % 2 or not 2 <= rotary_dim <= dim:
+            raise KernelError(f"angle tables must be float32 [positions, {rotary_dim // 2}] for {rotary_dim} rotated elements of {dim}")
+        _dev(cos, "cosines"), _dev(sin, "sines")
+        max_pos = cos.shape[0]
+        if ctx.max_kv_len > max_pos:
+            raise KernelError(f"a position of this step ({ctx.max_kv_len - 1}) lies beyond the angle tables ({max_pos} positions)")
+    if head_factor is not None:
+        _f32_vector(head_factor, num_heads, "per-head factors")
+    q = torch.empty((t, num_heads, dim), dtype=proj.dtype, device=proj.device)
+    check(lib().psb_attention_prepare(proj.data_ptr(), int(proj.stride(0)), _code(proj, "projection output"), _i32(ctx.positions, "positions").data_ptr(),
+                                      _i32(ctx.token_item, "token-to-item map").data_ptr(), table.data_ptr(), table.shape[1],
+                                      _ptr(cos), _ptr(sin), _ptr(head_factor), kv.data_ptr(), _code(kv, "cache entry"), q.data_ptr(),
+                                      t, num_heads, num_kv_heads, dim, vdim, page_size, kv.shape[0], max_pos, rotary_dim,
+                                      1 if interleaved else 0, -1.0 if unit_norm_eps is None else float(unit_norm_eps),
+                                      1 if values_are_keys else 0, _stream()), "attention_prepare")
+    return q
+
+
+MIN_GRU_CHUNK = 64  # portions of more than twice this many tokens run as chunks side by side
+
+
+def min_gru(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor, ctx, *, width: int) -> torch.Tensor:
+    """The minGRU recurrence over every portion of the step.  proj [T, >= 3W]: update-gate, candidate and output-gate
+    pre-activations in its first 3W columns (the tensor may be a column slice of a wider one); biases float32 [W];
+    state float32 [num_slots, W] (rows may be strided), read and brought up to date.  Returns S_t * silu(g_t) [T, W]."""
+    if not proj.is_cuda or proj.dim() != 2 or proj.shape[1] < 3 * width or proj.stride(1) != 1:
+        raise KernelError(f"minGRU: projection must be [T, >= {3 * width}] on the device with unit column stride, is {tuple(proj.shape)}")
+    t = proj.shape[0]
+    stride = _slot_rows(state, width, "minGRU state")
+    _f32_vector(bias_z, width, "update-gate bias"), _f32_vector(bias_x, width, "candidate bias")
+    out = torch.empty((t, width), dtype=proj.dtype, device=proj.device)
+    two_pass = ctx.max_new_tokens > 2 * MIN_GRU_CHUNK
+    chunk = MIN_GRU_CHUNK if two_pass else max(t, 1)
+    carry = start = None
+    if two_pass:
+        carry = torch.empty((t // chunk + ctx.num_items, width, 2), dtype=torch.float32, device=proj.device)
+        start = torch.empty((ctx.num_items, width), dtype=torch.float32, device=proj.device)
+    check(lib().psb_min_gru(proj.data_ptr(), int(proj.stride(0)), _code(proj, "projection output"), bias_z.data_ptr(),
+                            bias_x.data_ptr(), state.data_ptr(), stride, _i32(ctx.item_start, "item offsets").data_ptr(),
+                            _i32(ctx.slots, "slots").data_ptr(), _ptr(carry), _ptr(start), out.data_ptr(), ctx.num_items, t, width,
+                            state.shape[0], chunk, 1 if two_pass else 0, _stream()), "min_gru")
+    return out
+
+
+def clipped_glu(gate_up: torch.Tensor, limit: float, alpha: float = 1.702, offset: float = 1.0) -> torch.Tensor:
+    """[T, 2I] -> g * sigmoid(alpha * g) * (u + offset) with g = min(first half, limit), u = clamp(second half, +-limit)."""
+    _dev(gate_up, "gate/up projection")
+    t, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError(f"gate/up projection must have an even width, has {two_i}")
+    out = torch.empty((t, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    check(lib().psb_clipped_glu(gate_up.data_ptr(), _code(gate_up, "gate/up projection"), out.data_ptr(), t, two_i // 2,
+                                float(limit), float(alpha), float(offset), _stream()), "clipped_glu")
     return out

@@ -189,6 +189,18 @@ _SIGNATURES: dict[str, list] = {
     "psb_moe_gemm": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, P],
     # (y, y_dtype, pair_row, weight, shared, shared_dtype, gate, ldg, out, out_dtype, T, H, top, stream)
     "psb_moe_combine": [P, I, P, P, P, I, P, I, P, I, I, I, I, P],
+    # (x, dtype, mix, state, stride, positions, token_item, item_start, slots, y, T, W, num_slots, stream)
+    "psb_token_shift": [P, I, P, P, L, P, P, P, P, P, I, I, I, P],
+    # (a, b, dtype, gain_a, gain_b, out_f32, T, W, eps, weight, stream)
+    "psb_normed_pair_sum": [P, P, I, P, P, P, I, I, F, F, P],
+    # (proj, ld, dtype, positions, token_item, table, table_width, cos, sin, head_factor, kv, kv_dtype, q_out, T, hq, hkv, dim, vdim,
+    #  page_size, num_pages, max_positions, rotary_dim, interleaved, eps, values_are_keys, stream)
+    "psb_attention_prepare": [P, L, I, P, P, P, I, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, I, F, I, P],
+    # (proj, ld, dtype, bias_z, bias_x, state, stride, item_start, slots, carry, start, out, items, T, W, num_slots, chunk,
+    #  two_pass, stream)
+    "psb_min_gru": [P, L, I, P, P, P, L, P, P, P, P, P, I, I, I, I, I, I, P],
+    # (gate_up, dtype, out, T, I, limit, alpha, offset, stream)
+    "psb_clipped_glu": [P, I, P, I, I, F, F, F, P],
 }
 
 

@@ -1,4 +1,4 @@
-from . import attention, biased_attention, delta, embedding, ffn, gate, latent_attention, moe, norm, position, recurrent  # noqa: F401  (registers the built-in kinds)
+from . import attention, biased_attention, combined, delta, embedding, ffn, gate, latent_attention, min_gru, moe, norm, normed_attention, position, recurrent  # noqa: F401  (registers the built-in kinds)
 from .base import (CacheNeed, CacheView, FeedForward, FixedState, Gate, ItemView, Mixer, Norm, PagedKV, ParamSpec, Part,
                    PositionEncoding, StepContext)
 from .block import Block, register_arrangement

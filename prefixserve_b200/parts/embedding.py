@@ -21,6 +21,7 @@ class TokenEmbedding(Part):
         super().__init__(params)
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
+        self.scale = float(params.get("scale", 1.0))  # the rows are multiplied by this on their way into the float32 stream
         self.table: torch.Tensor | None = None
 
     def param_specs(self):
@@ -30,7 +31,7 @@ class TokenEmbedding(Part):
         self.table = tensors["weight"].contiguous()
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
-        return ops.embedding(token_ids, self.table)
+        return ops.embedding(token_ids, self.table, scale=self.scale)
 
 
 class HashedPairEmbedding(Part):

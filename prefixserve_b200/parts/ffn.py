@@ -1,5 +1,9 @@
 """Gated feed-forward: down(act(gate(x)) * up(x)), gate and up fused into one
-matrix (prefixserve/model/llama.py:120-121, prefixserve/model/weights.py:120-123)."""
+matrix (prefixserve/model/llama.py:120-121, prefixserve/model/weights.py:120-123).
+
+``activation``: ``silu``, ``gelu_tanh``, or ``clipped_swiglu``, in which both branches are clipped before they meet:
+g = min(gate, limit), u = clamp(up, -limit, limit), and the product is g * sigmoid(alpha * g) * (u + offset)
+(``limit`` required; ``gate_alpha`` defaults to 1.702 and ``up_offset`` to 1)."""
 
 from __future__ import annotations
 
@@ -19,8 +23,15 @@ class GatedMLP(FeedForward):
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
         self.activation = str(params.get("activation", "silu"))
-        if self.activation not in ops.ACTIVATIONS:
-            raise ValueError(f"activation {self.activation!r} is not built (one of {sorted(ops.ACTIVATIONS)})")
+        self.clipped = self.activation == "clipped_swiglu"
+        if self.clipped:
+            self.limit = float(params["limit"])
+            self.gate_alpha = float(params.get("gate_alpha", 1.702))
+            self.up_offset = float(params.get("up_offset", 1.0))
+            if not self.limit > 0:
+                raise ValueError(f"clipped_swiglu needs a positive limit, not {self.limit}")
+        elif self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r} is not built (one of {sorted(ops.ACTIVATIONS) + ['clipped_swiglu']})")
         self.w_gate_up: torch.Tensor | None = None
         self.w_down: torch.Tensor | None = None
 
@@ -38,6 +49,9 @@ class GatedMLP(FeedForward):
         self.w_down = tensors["down_proj"].contiguous()
 
     def forward(self, x, ctx: StepContext):
+        if self.clipped:
+            act = ops.clipped_glu(ops.linear(x, self.w_gate_up), self.limit, self.gate_alpha, self.up_offset)
+            return ops.last_product(act, self.w_down, ctx)
         return ops.last_product(ops.gated_linear(x, self.w_gate_up, self.activation), self.w_down, ctx)
 
 
