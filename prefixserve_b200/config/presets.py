@@ -105,6 +105,37 @@ PRESETS.update({
 })
 
 
+def _goganex(width: int, vocab: int, groups: int, heads: int, kv_heads: int, dim: int, ff: int, recurrent_width: int) -> dict:
+    """``groups`` times (attention, attention, attention, parallel), every layer with a feed-forward."""
+    rot = {"base": 500000.0, "dims": dim, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    attention = {"type": "attention", "mlp": mlp,
+                 "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": rot}}
+    parallel = {"type": "parallel", "mlp": mlp,
+                "mixer": {"left": {"heads": heads // 2, "kv_heads": kv_heads // 2, "dim": dim, "vdim": dim, "scale": dim ** -0.5},
+                          "right": {"width": recurrent_width}}}
+    return {"architecture": "Goganex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": [attention, attention, attention, parallel] * groups}
+
+
+PRESETS.update({
+    "goganex-tiny": {
+        "architecture": "Goganex", "vocab": 256, "width": 64, "norm": {"eps": 1e-6}, "embedding": {"scale": 2.0},
+        "loop": {"start": 0, "stop": 2, "times": 2},
+        "layers": [
+            {"type": "attention", "mlp": {"kind": "dense", "ff": 128, "limit": 2.0},
+             "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.25,
+                       "rot": {"base": 10000.0, "dims": 8, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 64}}}},
+            {"type": "parallel", "mlp": None,
+             "mixer": {"left": {"heads": 2, "kv_heads": 1, "dim": 16, "vdim": 16, "scale": 0.25}, "right": {"width": 48}}},
+        ],
+    },
+    # layer sizes of a 1B- and an 8B-class decoder (width, heads, feed-forward), for the benchmarks
+    "goganex-2048": _goganex(2048, 32768, 3, 32, 8, 64, 8192, 2048),
+    "goganex-4096": _goganex(4096, 32768, 2, 32, 8, 128, 14336, 4096),
+})
+
+
 def preset(name: str):
     """The typed configuration of a preset, read by its architecture's own reader."""
     try:
