@@ -767,6 +767,10 @@ NERENEX_SIZES = {"2048": ("nerenex-2048", "1b"), "4096": ("nerenex-4096", "8b")}
 # --workload gekopel: the design's preset and the preset of the closest model already here (Nerenex: layers of a recurrence
 # or an attention over a bounded span of keys, in the same order, at the same width and depth)
 GEKOPEL_SIZES = {"2048": ("gekopel-2048", "nerenex-2048"), "4096": ("gekopel-4096", "nerenex-4096")}
+# --workload goganex: the closest model already here is the Llama (attention over every earlier key with a rotation, a gated
+# feed-forward, pre-norm blocks), at the same width, heads, feed-forward size and number of layers
+GOGANEX_SIZES = {"2048": ("goganex-2048", "1b"), "4096": ("goganex-4096", "8b")}
+BESIDE = {"nerenex": "llama", "gekopel": "nerenex", "goganex": "llama"}
 
 
 def run_nerenex(args, design: str = "nerenex") -> dict:
@@ -775,7 +779,10 @@ def run_nerenex(args, design: str = "nerenex") -> dict:
     Llama of the same width and number of layers, device-timed, with the time of every kernel name in one prefill step
     and one decode step (torch profiler; those steps are not the timed ones).
     --workload gekopel: the same for the Gekopel design (delta rule, delta rule, chunked attention with a distance bias
-    and a sink; routed experts; sandwich-norm blocks) beside Nerenex at the same width and number of layers."""
+    and a sink; routed experts; sandwich-norm blocks) beside Nerenex at the same width and number of layers.
+    --workload goganex: the same for the Goganex design (token shift; unit-normed attention with a factor per head and a
+    sink, three layers of it, then attention whose keys are its values beside a minGRU; clipped gated feed-forward)
+    beside a Llama of the same width and number of layers."""
     import re
 
     import numpy as np
@@ -788,14 +795,14 @@ def run_nerenex(args, design: str = "nerenex") -> dict:
 
     prompt, context, batches = 2048, args.context if "--context" in sys.argv else 2048, (8, 32)
     steps, warmup = min(args.steps, 32), max(3, min(args.warmup, 8))
-    sizes = GEKOPEL_SIZES if design == "gekopel" else NERENEX_SIZES
+    sizes = {"gekopel": GEKOPEL_SIZES, "goganex": GOGANEX_SIZES}.get(design, NERENEX_SIZES)
     out = {"workload": design, "dtype": "bf16", "data": "synthetic", "prompt": prompt, "context": context, "steps": steps,
            "warmup": warmup, "timing": "CUDA events; weights of every model exceed L2", "peaks": peaks(), "sizes": {}}
     for size in ([args.model] if args.model in sizes else sorted(sizes)):
         own_name, llama_name = sizes[size]
         n_layers = len(PRESETS[own_name]["layers"])
         entry = out["sizes"][size] = {}
-        for which in ((design, "nerenex") if design == "gekopel" else ("nerenex", "llama")):
+        for which in (design, BESIDE[design]):
             if which == design:
                 cfg = preset(own_name)
                 vocab = cfg.vocab
@@ -946,11 +953,11 @@ def main() -> int:
     p.add_argument("--profile", action="store_true",
                    help="--timeline plus, per kernel, the bytes and flops it has to do in the step and the fraction of the "
                         "measured peak that its time inside the step amounts to")
-    p.add_argument("--workload", choices=["decode", "shared-prefix", "mixed", "nerenex", "gekopel"], default="decode",
+    p.add_argument("--workload", choices=["decode", "shared-prefix", "mixed", "nerenex", "gekopel", "goganex"], default="decode",
                    help="decode: the headline line.  shared-prefix: 64 requests over 4 system prefixes through the entry "
                         "point, prefix cache on and off.  mixed: steps of one 512-token prompt portion beside 64 decoded tokens.  "
                         "nerenex: prefill and decode of the Nerenex design beside a Llama of the same width and depth (--model 2048|4096).  "
-                        "gekopel: the same for the Gekopel design beside Nerenex")
+                        "gekopel: the same for the Gekopel design beside Nerenex.  goganex: the same for the Goganex design beside a Llama")
     p.add_argument("--model", choices=sorted(SIZES) + sorted(NERENEX_SIZES), default=None,
                    help="layer sizes for --workload shared-prefix (8b) / mixed (3b), and for --only decode (the headline stays 1b)")
     p.add_argument("--requests", type=int, default=64, help="requests of --workload shared-prefix")
@@ -986,7 +993,7 @@ def main() -> int:
             return 0
         if _no_device(args):
             return 1
-        if args.workload in ("nerenex", "gekopel"):
+        if args.workload in ("nerenex", "gekopel", "goganex"):
             result = run_nerenex(args, args.workload)
             print(json.dumps(result))
             return 0

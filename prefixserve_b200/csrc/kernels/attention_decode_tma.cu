@@ -81,7 +81,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
                             const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ item_start,
                             const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                             float* __restrict__ part_ml, int hq, int hkv, int page_shift, int window, float scale, int chunk,
-                            int max_splits, int all_single) {
+                            int max_splits, int all_single, const float* __restrict__ sink) {
   using Sh = Shape<D>;
   constexpr int STAGES = Sh::STAGES;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -319,7 +319,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
     }
     const int head = h * G + row;
     if (max_splits == 1) {
-      out[((size_t)t0 * hq + head) * D + d] = __float2bfloat16_rn(acc / l);
+      // the only range: a sink joins the denominator here (with several ranges, in the kernel that joins them)
+      out[((size_t)t0 * hq + head) * D + d] =
+          __float2bfloat16_rn(sink ? acc * sink_quotient2(m_safe, l, sink[head] * PSB_LOG2E) : acc / l);
     } else {
       const size_t slot = ((size_t)item * hq + head) * max_splits + split;
       part_o[slot * D + d] = acc;
@@ -331,7 +333,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __
 template <int D>
 int launch(const CUtensorMap& map, const void* q, const void* table, int table_width, const void* item_start, const void* kv_len,
            void* out, void* part_o, void* part_ml, int num_items, int hq, int hkv, int page_shift, int window, float scale,
-           int chunk, int max_splits, int all_single, cudaStream_t stream) {
+           int chunk, int max_splits, int all_single, const float* sink, cudaStream_t stream) {
   static PsbPerDevice configured;
   if (!configured.get()) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<D>::SMEM_BYTES);
@@ -340,7 +342,8 @@ int launch(const CUtensorMap& map, const void* q, const void* table, int table_w
   }
   psb_launch(attention_decode_tma_kernel<D>, dim3(max_splits, hkv, num_items), dim3(THREADS), (size_t)Shape<D>::SMEM_BYTES, stream,
              map, (const __nv_bfloat16*)q, (const int32_t*)table, table_width, (const int32_t*)item_start, (const int32_t*)kv_len,
-             (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, hq, hkv, page_shift, window, scale, chunk, max_splits, all_single);
+             (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, hq, hkv, page_shift, window, scale, chunk, max_splits, all_single,
+             sink);
   return 0;
 }
 
@@ -359,7 +362,7 @@ PSB_API int psb_attention_decode_tma_supported(int hq, int hkv, int D, int page_
 PSB_API int psb_attention_decode_tma_bf16(const void* q, const void* kv, const void* table, int table_width, const void* item_start,
                                           const void* kv_len, void* out, void* part_o, void* part_ml, int num_items, int hq,
                                           int hkv, int D, int page_size, long long num_pages, int window, float scale, int chunk,
-                                          int max_splits, int all_single, cudaStream_t stream) {
+                                          int max_splits, int all_single, const void* sink, cudaStream_t stream) {
   if (!psb_attention_decode_tma_supported(hq, hkv, D, page_size))
     PSB_REFUSE("attention_decode_tma: hq=%d hkv=%d D=%d pages of %d are not built (heads of 64 or 128, groups up to 16, pages a power of two from 16)", hq, hkv, D, page_size);
   if (window < 0 || table_width < 1 || num_pages < 1) PSB_REFUSE("attention_decode_tma: bad sizes (window=%d table_width=%d)", window, table_width);
@@ -378,8 +381,8 @@ PSB_API int psb_attention_decode_tma_bf16(const void* q, const void* kv, const v
   if (r == -1) PSB_REFUSE("attention_decode_tma: the driver does not export cuTensorMapEncodeTiled");
   if (r != 0) PSB_REFUSE("attention_decode_tma: cuTensorMapEncodeTiled failed with code %d", r);
   int rc;
-  if (D == 64) rc = launch<64>(map, q, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, page_shift, window, scale, chunk, max_splits, all_single, stream);
-  else rc = launch<128>(map, q, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, page_shift, window, scale, chunk, max_splits, all_single, stream);
+  if (D == 64) rc = launch<64>(map, q, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, page_shift, window, scale, chunk, max_splits, all_single, (const float*)sink, stream);
+  else rc = launch<128>(map, q, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, page_shift, window, scale, chunk, max_splits, all_single, (const float*)sink, stream);
   if (rc) return rc;
   PSB_LAUNCH_CHECK("attention_decode_tma");
   return 0;

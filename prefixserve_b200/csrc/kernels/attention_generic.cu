@@ -28,7 +28,8 @@ template <typename T, typename TKV>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, const int32_t* __restrict__ table,
                          int table_width, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_item,
-                         T* __restrict__ out, int T_tokens, int hq, int hkv, int D, int page_size, int window, float scale) {
+                         T* __restrict__ out, int T_tokens, int hq, int hkv, int D, int page_size, int window, float scale,
+                         const float* __restrict__ sink) {
   __shared__ float qs[WARPS][MAX_D];
   pdl_trigger();
   pdl_wait();
@@ -91,7 +92,8 @@ attention_generic_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, co
       }
     }
   }
-  const float inv = 1.f / l;
+  // with a sink (a score per head that joins the denominator without a value) the quotient is taken in powers of two
+  const float inv = sink ? sink_quotient2(m * PSB_LOG2E, l, sink[h] * PSB_LOG2E) : 1.f / l;
   T* orow = out + ((size_t)t * hq + h) * D;
 #pragma unroll
   for (int i = 0; i < MAX_D / 32; ++i) {
@@ -104,7 +106,7 @@ attention_generic_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, co
 
 PSB_API int psb_attention_generic(const void* q, int dtype, const void* kv, int kv_dtype, const void* table,
                                   int table_width, const void* positions, const void* token_item, void* out, int T,
-                                  int hq, int hkv, int D, int page_size, int window, float scale, cudaStream_t stream) {
+                                  int hq, int hkv, int D, int page_size, int window, float scale, const void* sink, cudaStream_t stream) {
   if (T < 0 || hq < 1 || hkv < 1 || hq % hkv) PSB_REFUSE("attention: %d query heads cannot share %d key/value heads", hq, hkv);
   if (D < 1 || D > MAX_D) PSB_REFUSE("attention: head size %d is outside [1, %d]", D, MAX_D);
   if (page_size < 1 || table_width < 1) PSB_REFUSE("attention: bad paging (page_size=%d width=%d)", page_size, table_width);
@@ -117,7 +119,7 @@ PSB_API int psb_attention_generic(const void* q, int dtype, const void* kv, int 
     PSB_DISPATCH_DTYPE(kv_dtype, TKV, {
       psb_launch(attention_generic_kernel<T_, TKV>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream,
           (const T_*)q, (const TKV*)kv, (const int32_t*)table, table_width, (const int32_t*)positions,
-          (const int32_t*)token_item, (T_*)out, T, hq, hkv, D, page_size, window, scale);
+          (const int32_t*)token_item, (T_*)out, T, hq, hkv, D, page_size, window, scale, (const float*)sink);
     });
   });
   PSB_LAUNCH_CHECK("attention_generic");

@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kv,
                          const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ item_start,
                          const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, int num_items, int hq, int hkv,
-                         int page_shift, int window, float scale, int skip_single) {
+                         int page_shift, int window, float scale, int skip_single, const float* __restrict__ sink) {
   using Shape = PrefillShape<D>;
   constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES, KP = 2 * (D / 32);
   constexpr int ROWS = WARPS * 16 * MT;  // rows per CTA
@@ -488,7 +488,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       l += __shfl_xor_sync(0xffffffffu, l, 1);
       l += __shfl_xor_sync(0xffffffffu, l, 2);
       if (tok[mt][r] < 0) continue;
-      const float inv = 1.f / l;
+      // a sink (a score per head without a value) joins the denominator here, where the row's sum is complete
+      const float inv = sink ? sink_quotient2(st[mt].m[r], l, sink[head[mt][r]] * PSB_LOG2E) : 1.f / l;
       __nv_bfloat16* orow = out + ((size_t)(t0 + tok[mt][r]) * hq + head[mt][r]) * D;
       // this lane owns dims [2t*D/8, (2t+2)*D/8): accumulator column 2t is the first half, 2t+1 the second
 #pragma unroll
@@ -508,7 +509,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ item_start,
                         const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int hq, int hkv, int page_shift, int window, float scale, int chunk,
-                        int max_splits, int all_single) {
+                        int max_splits, int all_single, const float* __restrict__ sink) {
   using Shape = DecodeShape<D>;
   constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES, KP = 2 * (D / 32);
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -673,7 +674,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     }
     const int head = h * G + row;
     if (max_splits == 1) {
-      out[((size_t)t0 * hq + head) * D + d] = __float2bfloat16_rn(o / l);
+      // the only range: a sink joins the denominator here (with several ranges, in the kernel that joins them)
+      out[((size_t)t0 * hq + head) * D + d] =
+          __float2bfloat16_rn(sink ? o * sink_quotient2(m_safe, l, sink[head] * PSB_LOG2E) : o / l);
     } else {
       const size_t slot = ((size_t)item * hq + head) * max_splits + split;
       part_o[slot * D + d] = o;
@@ -691,7 +694,8 @@ template <int D, int MW>
 __global__ void __launch_bounds__(32 * MW)
 attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                        const int32_t* __restrict__ item_start, const int32_t* __restrict__ kv_len,
-                       __nv_bfloat16* __restrict__ out, int hq, int window, int chunk, int max_splits, int all_single) {
+                       __nv_bfloat16* __restrict__ out, int hq, int window, int chunk, int max_splits, int all_single,
+                       const float* __restrict__ sink) {
   __shared__ float sum_o[MW][D];
   __shared__ float sum_l[MW];
   pdl_trigger();
@@ -776,7 +780,8 @@ attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict
       for (int i = 0; i < D / 32; ++i) o[i] += sum_o[w][lane + 32 * i];
     }
   }
-  const float inv = 1.f / l;
+  // a sink is one more range with a sum of one and no output; l and o refer to the exponent m_safe
+  const float inv = sink ? sink_quotient2(m_safe, l, sink[head] * PSB_LOG2E) : 1.f / l;
 #pragma unroll
   for (int i = 0; i < D / 32; ++i)
     out[((size_t)t0 * hq + head) * D + lane + 32 * i] = __float2bfloat16_rn(o[i] * inv);
@@ -785,13 +790,14 @@ attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict
 // The merge with one warp up to eight ranges (one round of loads), four warps beyond.
 template <int D>
 void launch_merge(const float* part_o, const float* part_ml, const int32_t* item_start, const int32_t* kv_len, __nv_bfloat16* out,
-                  int num_items, int hq, int window, int chunk, int max_splits, int all_single, cudaStream_t stream) {
+                  int num_items, int hq, int window, int chunk, int max_splits, int all_single, const float* sink,
+                  cudaStream_t stream) {
   if (max_splits <= 8)
     psb_launch(attention_merge_kernel<D, 1>, dim3(hq, num_items), dim3(32), 0, stream, part_o, part_ml, item_start, kv_len, out, hq,
-               window, chunk, max_splits, all_single);
+               window, chunk, max_splits, all_single, sink);
   else
     psb_launch(attention_merge_kernel<D, 4>, dim3(hq, num_items), dim3(128), 0, stream, part_o, part_ml, item_start, kv_len, out, hq,
-               window, chunk, max_splits, all_single);
+               window, chunk, max_splits, all_single, sink);
 }
 
 int check_common(const char* who, int hq, int hkv, int D, int page_size, int table_width, int window) {
@@ -807,7 +813,7 @@ int check_common(const char* who, int hq, int hkv, int D, int page_size, int tab
 PSB_API int psb_attention_prefill_bf16(const void* q, const void* kv, const void* table, int table_width,
                                        const void* item_start, const void* kv_len, void* out, int num_items, int num_tiles,
                                        int hq, int hkv, int D, int page_size, int window, float scale, int skip_single,
-                                       cudaStream_t stream) {
+                                       const void* sink, cudaStream_t stream) {
   if (int rc = check_common("attention_prefill", hq, hkv, D, page_size, table_width, window)) return rc;
   if (num_items < 0 || num_tiles < 0) PSB_REFUSE("attention_prefill: negative sizes");
   if (num_items == 0 || num_tiles == 0) return 0;
@@ -828,7 +834,7 @@ PSB_API int psb_attention_prefill_bf16(const void* q, const void* kv, const void
     psb_launch(attention_prefill_kernel<DD, MT>, grid, dim3(WARPS * 32), (size_t)PrefillShape<DD>::SMEM_BYTES, stream, \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width,                       \
         (const int32_t*)item_start, (const int32_t*)kv_len, (__nv_bfloat16*)out, num_items, hq, hkv, page_shift,     \
-        window, scale, skip_single);                                                                                 \
+        window, scale, skip_single, (const float*)sink);                                                             \
   } while (0)
   if (D == 64) PSB_PREFILL(64, 2); else PSB_PREFILL(128, 1);
 #undef PSB_PREFILL
@@ -842,7 +848,7 @@ PSB_API int psb_attention_prefill_rows_per_cta(int D) { return D == 64 ? WARPS *
 PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void* table, int table_width,
                                       const void* item_start, const void* kv_len, void* out, void* part_o, void* part_ml,
                                       int num_items, int hq, int hkv, int D, int page_size, int window, float scale, int chunk,
-                                      int max_splits, int all_single, cudaStream_t stream) {
+                                      int max_splits, int all_single, const void* sink, cudaStream_t stream) {
   if (int rc = check_common("attention_decode", hq, hkv, D, page_size, table_width, window)) return rc;
   if (hq / hkv > 16) PSB_REFUSE("attention_decode: groups of more than 16 query heads are not built");
   // a range is walked in tiles of 16 keys that its warps take in turn: it may end after any whole tile
@@ -867,10 +873,10 @@ PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void*
     psb_launch(attention_decode_kernel<DD>, grid, dim3(WARPS * 32), (size_t)DecodeShape<DD>::SMEM_BYTES, stream, \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table, table_width, (const int32_t*)item_start, \
         (const int32_t*)kv_len, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, hq, hkv, page_shift, window, scale, \
-        chunk, max_splits, all_single);                                                                              \
+        chunk, max_splits, all_single, (const float*)sink);                                                          \
     if (max_splits > 1)                                                                                              \
       launch_merge<DD>((const float*)part_o, (const float*)part_ml, (const int32_t*)item_start, (const int32_t*)kv_len, \
-                       (__nv_bfloat16*)out, num_items, hq, window, chunk, max_splits, all_single, stream);             \
+                       (__nv_bfloat16*)out, num_items, hq, window, chunk, max_splits, all_single, (const float*)sink, stream); \
   } while (0)
   if (D == 64) PSB_DECODE(64); else PSB_DECODE(128);
 #undef PSB_DECODE
@@ -882,17 +888,17 @@ PSB_API int psb_attention_decode_bf16(const void* q, const void* kv, const void*
 // results in the same layout.
 PSB_API int psb_attention_decode_merge_bf16(const void* part_o, const void* part_ml, const void* item_start, const void* kv_len,
                                             void* out, int num_items, int hq, int D, int window, int chunk, int max_splits,
-                                            int all_single, cudaStream_t stream) {
+                                            int all_single, const void* sink, cudaStream_t stream) {
   if (D != 64 && D != 128) PSB_REFUSE("attention_merge: head size %d is not built", D);
   if (max_splits < 2 || max_splits > 1024 || !part_o || !part_ml) PSB_REFUSE("attention_merge: %d key ranges, or their scratch is missing", max_splits);
   if (num_items <= 0) return 0;
   if (num_items > 65535) PSB_REFUSE("attention_merge: batch too large");
   if (D == 64)
     launch_merge<64>((const float*)part_o, (const float*)part_ml, (const int32_t*)item_start, (const int32_t*)kv_len,
-                     (__nv_bfloat16*)out, num_items, hq, window, chunk, max_splits, all_single, stream);
+                     (__nv_bfloat16*)out, num_items, hq, window, chunk, max_splits, all_single, (const float*)sink, stream);
   else
     launch_merge<128>((const float*)part_o, (const float*)part_ml, (const int32_t*)item_start, (const int32_t*)kv_len,
-                      (__nv_bfloat16*)out, num_items, hq, window, chunk, max_splits, all_single, stream);
+                      (__nv_bfloat16*)out, num_items, hq, window, chunk, max_splits, all_single, (const float*)sink, stream);
   PSB_LAUNCH_CHECK("attention_merge");
   return 0;
 }
@@ -934,5 +940,5 @@ PSB_API int psb_attention_decode_bf16_static(const void* q, const void* kv, cons
   float* part_o = g_decode_scratch_addr[device];
   float* part_ml = part_o + ranges * (unsigned long long)D;
   return psb_attention_decode_bf16(q, kv, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, D,
-                                   page_size, window, scale, chunk, max_splits, all_single, stream);
+                                   page_size, window, scale, chunk, max_splits, all_single, nullptr, stream);
 }

@@ -8,9 +8,14 @@
 //   a factor per query head (optional), so that a head's scores come out multiplied by it;
 //   the query written to q_out [T, hq, dim]; the key, then the value, to the token's row of the cache entry
 //     [num_pages, 1, hkv, page_size, dim + vdim], the value being the head's own projection or, with
-//     ``values_are_keys``, the key as it was projected (before rotation and norm).
+//     ``values_are_keys``, the key as it was projected (before rotation and norm).  With ``split_planes`` (vdim == dim)
+//     the entry is [num_pages, 2, hkv, page_size, dim] instead, keys in plane 0 and values in plane 1: the layout of
+//     the attention kernels that read keys and values as separate tiles.
 //
-// One block per token, a warp per head in turn; the head lies in the warp's shared-memory row between the steps.
+// Two kernels.  The general one: one block per token, a warp per head in turn; the head lies in the warp's
+// shared-memory row between the steps.  The other, for heads of 64, 128 or 256 elements whose rotation (if any) pairs
+// neighbours: a warp per (token, head), the head in registers (every lane a run of dim/32 elements, which holds whole
+// pairs), one wide load and one wide store per lane and row.
 // Rotation, statistics and factors are float32; storage is float32 or bfloat16.
 #include "common.cuh"
 
@@ -25,7 +30,8 @@ attention_prepare_kernel(const T* __restrict__ proj, long long ld, const int32_t
                          const int32_t* __restrict__ token_item, const int32_t* __restrict__ table, int table_width,
                          const float* __restrict__ cos_t, const float* __restrict__ sin_t, const float* __restrict__ head_factor,
                          TKV* __restrict__ kv, T* __restrict__ q_out, int hq, int hkv, int dim, int vdim, int page_size,
-                         int num_pages, int max_positions, int rotary_dim, int interleaved, float eps, int values_are_keys) {
+                         int num_pages, int max_positions, int rotary_dim, int interleaved, float eps, int values_are_keys,
+                         int split_planes) {
   __shared__ float rows[PREP_WARPS][PREP_MAX_D];
   pdl_trigger();
   pdl_wait();
@@ -69,24 +75,112 @@ attention_prepare_kernel(const T* __restrict__ proj, long long ld, const int32_t
       for (int d = lane; d < dim; d += 32) dst[d] = from_float<T>(mine[d] * factor * f);
     } else if (page_ok) {
       const int g = head - hq;
-      TKV* dst = kv + (((size_t)page * hkv + g) * page_size + (size_t)(p % page_size)) * rw;
+      const size_t slot = (size_t)(p % page_size);
+      TKV* dst = split_planes ? kv + ((((size_t)page * 2) * hkv + g) * page_size + slot) * dim
+                              : kv + (((size_t)page * hkv + g) * page_size + slot) * rw;
+      TKV* vdst = split_planes ? dst + (size_t)hkv * page_size * dim : dst + dim;
       for (int d = lane; d < dim; d += 32) dst[d] = from_float<TKV>(mine[d] * factor);
       const T* vsrc = values_are_keys ? src : row + qw + kw + (size_t)g * vdim;
-      for (int d = lane; d < vdim; d += 32) dst[dim + d] = from_float<TKV>(to_float<T>(vsrc[d]));
+      for (int d = lane; d < vdim; d += 32) vdst[d] = from_float<TKV>(to_float<T>(vsrc[d]));
     }
     __syncwarp();
   }
 }
 
+// A run of N elements that is loaded and stored as one piece.
+template <typename T, int N>
+struct alignas(sizeof(T) * N) Run {
+  T v[N];
+};
+
+// grid: T * ceil((hq + hkv) / PREP_WARPS) blocks; warp w of block b: token b / groups, head (b % groups) * PREP_WARPS + w.
+template <typename T, typename TKV, int DIM>
+__global__ void __launch_bounds__(PREP_WARPS * 32)
+attention_prepare_rows_kernel(const T* __restrict__ proj, long long ld, const int32_t* __restrict__ positions,
+                              const int32_t* __restrict__ token_item, const int32_t* __restrict__ table, int table_width,
+                              const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                              const float* __restrict__ head_factor, TKV* __restrict__ kv, T* __restrict__ q_out, int hq, int hkv,
+                              int page_size, int num_pages, int max_positions, int rotary_dim, float eps, int values_are_keys,
+                              int split_planes, int groups) {
+  constexpr int N = DIM / 32;
+  pdl_trigger();
+  const int t = blockIdx.x / groups;
+  const int head = (blockIdx.x - t * groups) * PREP_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  // positions and tables are inputs of the step: they may be read before the preceding kernel has finished
+  const int p = positions[t];
+  const int page = table[(size_t)token_item[t] * table_width + p / page_size];
+  pdl_wait();
+  if (head >= hq + hkv) return;
+  const bool is_q = head < hq;
+  const T* row = proj + (size_t)t * ld;
+  const T* src = row + (size_t)head * DIM;
+  const Run<T, N> raw = *reinterpret_cast<const Run<T, N>*>(src + lane * N);
+  float x[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) x[i] = to_float<T>(raw.v[i]);
+  if (cos_t != nullptr && p >= 0 && p < max_positions) {
+    const float* cs = cos_t + (size_t)p * (rotary_dim / 2);
+    const float* sn = sin_t + (size_t)p * (rotary_dim / 2);
+#pragma unroll
+    for (int i = 0; i < N; i += 2) {
+      const int d = lane * N + i;  // even: the pair (d, d + 1) turns by angle d / 2
+      if (d < rotary_dim) {
+        float o1, o2;
+        rotate_pair(x[i], x[i + 1], cs[d >> 1], sn[d >> 1], o1, o2);
+        x[i] = o1;
+        x[i + 1] = o2;
+      }
+    }
+  }
+  float factor = 1.f;
+  if (eps >= 0.f) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) ss = fmaf(x[i], x[i], ss);
+    factor = 1.f / sqrtf(warp_sum(ss) / (float)DIM + eps);
+  }
+  if (is_q) {
+    const float f = head_factor ? head_factor[head] : 1.f;
+    Run<T, N> o;
+#pragma unroll
+    for (int i = 0; i < N; ++i) o.v[i] = from_float<T>(x[i] * factor * f);
+    *reinterpret_cast<Run<T, N>*>(q_out + ((size_t)t * hq + head) * DIM + lane * N) = o;
+    return;
+  }
+  if (page < 0 || page >= num_pages) return;  // tables are checked on the host; never write outside the pool
+  const int g = head - hq;
+  const size_t slot = (size_t)(p % page_size);
+  TKV* dst = split_planes ? kv + ((((size_t)page * 2) * hkv + g) * page_size + slot) * DIM
+                          : kv + (((size_t)page * hkv + g) * page_size + slot) * (2 * DIM);
+  TKV* vdst = split_planes ? dst + (size_t)hkv * page_size * DIM : dst + DIM;
+  Run<TKV, N> k;
+#pragma unroll
+  for (int i = 0; i < N; ++i) k.v[i] = from_float<TKV>(x[i] * factor);
+  *reinterpret_cast<Run<TKV, N>*>(dst + lane * N) = k;
+  Run<T, N> vin = raw;
+  if (!values_are_keys) vin = *reinterpret_cast<const Run<T, N>*>(row + (size_t)(hq + hkv) * DIM + (size_t)g * DIM + lane * N);
+  Run<TKV, N> v;
+#pragma unroll
+  for (int i = 0; i < N; ++i) v.v[i] = from_float<TKV>(to_float<T>(vin.v[i]));
+  *reinterpret_cast<Run<TKV, N>*>(vdst + lane * N) = v;
+}
+
 }  // namespace
 
+#define PSB_PREP_ROWS(DD)                                                                                              \
+  psb_launch(attention_prepare_rows_kernel<T_, TKV, DD>, dim3((unsigned)blocks), dim3(PREP_WARPS * 32), 0, stream,     \
+             (const T_*)proj, ld, (const int32_t*)positions, (const int32_t*)token_item, (const int32_t*)table,        \
+             table_width, (const float*)cos_t, (const float*)sin_t, (const float*)head_factor, (TKV*)kv, (T_*)q_out,   \
+             hq, hkv, page_size, num_pages, max_positions, rotary_dim, eps, values_are_keys, split_planes, groups)
+
 // (proj, ld, dtype, positions, token_item, table, table_width, cos, sin, head_factor, kv, kv_dtype, q_out, T, hq, hkv, dim, vdim,
-//  page_size, num_pages, max_positions, rotary_dim, interleaved, eps, values_are_keys, stream)
+//  page_size, num_pages, max_positions, rotary_dim, interleaved, eps, values_are_keys, split_planes, stream)
 PSB_API int psb_attention_prepare(const void* proj, long long ld, int dtype, const void* positions, const void* token_item, const void* table,
                                   int table_width, const void* cos_t, const void* sin_t, const void* head_factor, void* kv,
                                   int kv_dtype, void* q_out, int T, int hq, int hkv, int dim, int vdim, int page_size,
                                   int num_pages, int max_positions, int rotary_dim, int interleaved, float eps,
-                                  int values_are_keys, cudaStream_t stream) {
+                                  int values_are_keys, int split_planes, cudaStream_t stream) {
   if (T < 0 || hq < 1 || hkv < 1 || dim < 1 || dim > PREP_MAX_D || vdim < 1 || page_size < 1 || table_width < 1 || num_pages < 1)
     PSB_REFUSE("attention_prepare: bad sizes (heads %d/%d, sizes %d/%d, at most %d)", hq, hkv, dim, vdim, PREP_MAX_D);
   if (ld < (long long)(hq + hkv) * dim + (values_are_keys ? 0 : (long long)hkv * vdim)) PSB_REFUSE("attention_prepare: row stride %lld is shorter than the row", ld);
@@ -94,13 +188,35 @@ PSB_API int psb_attention_prepare(const void* proj, long long ld, int dtype, con
   if ((cos_t == nullptr) != (sin_t == nullptr)) PSB_REFUSE("attention_prepare: cosines and sines come together");
   if (cos_t && (rotary_dim < 2 || rotary_dim % 2 || rotary_dim > dim || max_positions < 1))
     PSB_REFUSE("attention_prepare: %d rotated elements of %d", rotary_dim, dim);
+  if (split_planes && vdim != dim) PSB_REFUSE("attention_prepare: keys and values in planes of their own need vdim == dim, not %d and %d", vdim, dim);
   if (T == 0) return 0;
+  // heads in registers: sizes that give every lane an even run, a rotation (if any) of neighbours, rows that allow wide loads
+  const bool rows_fit = vdim == dim && (dim == 64 || dim == 128 || dim == 256) && (cos_t == nullptr || interleaved);
+  if (rows_fit) {
+    const int groups = (hq + hkv + PREP_WARPS - 1) / PREP_WARPS;
+    const long long blocks = (long long)T * groups;
+    bool done = false;
+    PSB_DISPATCH_DTYPE(dtype, T_, {
+      PSB_DISPATCH_DTYPE(kv_dtype, TKV, {
+        const size_t in_run = sizeof(T_) * (size_t)(dim / 32), out_run = sizeof(TKV) * (size_t)(dim / 32);
+        if (blocks <= 0x7fffffffLL && (uintptr_t)proj % in_run == 0 && ((size_t)ld * sizeof(T_)) % in_run == 0 &&
+            (uintptr_t)q_out % in_run == 0 && (uintptr_t)kv % out_run == 0) {
+          if (dim == 64) PSB_PREP_ROWS(64); else if (dim == 128) PSB_PREP_ROWS(128); else PSB_PREP_ROWS(256);
+          done = true;
+        }
+      });
+    });
+    if (done) {
+      PSB_LAUNCH_CHECK("attention_prepare");
+      return 0;
+    }
+  }
   PSB_DISPATCH_DTYPE(dtype, T_, {
     PSB_DISPATCH_DTYPE(kv_dtype, TKV, {
       psb_launch(attention_prepare_kernel<T_, TKV>, dim3(T), dim3(PREP_WARPS * 32), 0, stream, (const T_*)proj, ld,
                  (const int32_t*)positions, (const int32_t*)token_item, (const int32_t*)table, table_width, (const float*)cos_t,
                  (const float*)sin_t, (const float*)head_factor, (TKV*)kv, (T_*)q_out, hq, hkv, dim, vdim, page_size, num_pages,
-                 max_positions, rotary_dim, interleaved, eps, values_are_keys);
+                 max_positions, rotary_dim, interleaved, eps, values_are_keys, split_planes);
     });
   });
   PSB_LAUNCH_CHECK("attention_prepare");

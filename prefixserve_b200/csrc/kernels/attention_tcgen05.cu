@@ -117,7 +117,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ item_start,
                                  const int32_t* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, int num_items, int hq,
                                  int hkv, int page_shift, int window, float scale, int skip_single, int rows_per_cta,
-                                 int kv_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+                                 int kv_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                                 const float* __restrict__ sink) {
   using Sh = Shape<D>;
   constexpr int KB = Sh::KB, NB = Sh::S_BUFS, STAGES = Sh::STAGES;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -572,7 +573,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         fence_before();
       } else if (ok) {
         fence_after();
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        // a sink (a score per head without a value) joins the denominator here, where the row's sum is complete
+        const float inv = l_run > 0.f ? (sink ? sink_quotient2(m_run * c, l_run, sink[head] * PSB_LOG2E) : 1.f / l_run) : 0.f;
         __nv_bfloat16* dst = out + ((size_t)(t0 + row) * hq + head) * D;
 #pragma unroll 1
         for (int cc = 0; cc < D / 32; ++cc) {
@@ -611,7 +613,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 template <int D>
 __global__ void attention_prefill_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                const int32_t* __restrict__ token_item, const int32_t* __restrict__ item_start,
-                                               __nv_bfloat16* __restrict__ out, int T, int hq, int kv_splits, int skip_single) {
+                                               __nv_bfloat16* __restrict__ out, int T, int hq, int kv_splits, int skip_single,
+                                               const float* __restrict__ sink) {
   pdl_trigger();
   const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   const int row = unit / hq, head = unit - row * hq;
@@ -625,9 +628,10 @@ __global__ void attention_prefill_merge_kernel(const float* __restrict__ part_o,
   const size_t base = ((size_t)row * hq + head) * kv_splits;
   const float e = lane < kv_splits ? part_ml[(base + lane) * 2] : -INFINITY;
   const float l = lane < kv_splits ? part_ml[(base + lane) * 2 + 1] : 0.f;
-  const float top = warp_max(e);
+  const float s2 = sink ? sink[head] * PSB_LOG2E : -INFINITY;  // the sink is one more range, with a sum of one and no output
+  const float top = fmaxf(warp_max(e), s2);
   float w = (l > 0.f && e != -INFINITY) ? ex2(e - top) : 0.f;
-  const float total = warp_sum(w * l);
+  const float total = warp_sum(w * l) + (sink ? exp2f(s2 - top) : 0.f);
   const float inv = total > 0.f ? 1.f / total : 0.f;
   float acc[D / 32];
 #pragma unroll
@@ -647,7 +651,7 @@ template <int D>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, const void* table, int table_width, const void* item_start,
            const void* kv_len, void* out, int num_items, int num_pairs, int hq, int hkv, int page_shift, int window,
            float scale, int skip_single, int rows_per_cta, int kv_splits, void* part_o, void* part_ml, const void* token_item,
-           int T, cudaStream_t stream) {
+           int T, const float* sink, cudaStream_t stream) {
   static PsbPerDevice configured; 
   if (!configured.get()) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
@@ -656,12 +660,13 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, const void* tabl
   }
   psb_launch(attention_prefill_tcgen05_kernel<D>, dim3(hq, num_pairs, kv_splits), dim3(THREADS), (size_t)smem_bytes<D>(), stream, map_q, map_kv,
              (const int32_t*)table, table_width, (const int32_t*)item_start, (const int32_t*)kv_len, (__nv_bfloat16*)out,
-             num_items, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, kv_splits, (float*)part_o, (float*)part_ml);
+             num_items, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, kv_splits, (float*)part_o, (float*)part_ml,
+             kv_splits > 1 ? (const float*)nullptr : sink);
   if (kv_splits > 1) {
     const long long units = (long long)T * hq;
     psb_launch(attention_prefill_merge_kernel<D>, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, stream, (const float*)part_o,
                (const float*)part_ml, (const int32_t*)token_item, (const int32_t*)item_start, (__nv_bfloat16*)out, T, hq, kv_splits,
-               skip_single);
+               skip_single, sink);
   }
   return 0;
 }
@@ -688,7 +693,7 @@ PSB_API int psb_attention_prefill_tcgen05(const void* q, const void* kv, const v
                                           const void* kv_len, void* out, int num_items, int num_pairs, int T, int hq, int hkv,
                                           int D, int page_size, long long num_pages, int window, float scale, int skip_single,
                                           int rows_per_cta, int kv_splits, void* part_o, void* part_ml, const void* token_item,
-                                          cudaStream_t stream) {
+                                          const void* sink, cudaStream_t stream) {
   if (kv_splits < 1 || kv_splits > 32 || (kv_splits > 1 && (!part_o || !part_ml || !token_item)))
     PSB_REFUSE("attention_prefill_tcgen05: %d key ranges (1 to 32), or their scratch is missing", kv_splits);
   if (rows_per_cta != ROWS_PER_CTA && rows_per_cta != TILE_M) PSB_REFUSE("attention_prefill_tcgen05: a CTA owns %d or %d rows, not %d", ROWS_PER_CTA, TILE_M, rows_per_cta);
@@ -709,8 +714,8 @@ PSB_API int psb_attention_prefill_tcgen05(const void* q, const void* kv, const v
   if (r == -1) PSB_REFUSE("attention_prefill_tcgen05: the driver does not export cuTensorMapEncodeTiled");
   if (r != 0) PSB_REFUSE("attention_prefill_tcgen05: cuTensorMapEncodeTiled failed with code %d", r);
   int rc;
-  if (D == 64) rc = launch<64>(map_q, map_kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, kv_splits, part_o, part_ml, token_item, T, stream);
-  else rc = launch<128>(map_q, map_kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, kv_splits, part_o, part_ml, token_item, T, stream);
+  if (D == 64) rc = launch<64>(map_q, map_kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, kv_splits, part_o, part_ml, token_item, T, (const float*)sink, stream);
+  else rc = launch<128>(map_q, map_kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, hq, hkv, page_shift, window, scale, skip_single, rows_per_cta, kv_splits, part_o, part_ml, token_item, T, (const float*)sink, stream);
   if (rc) return rc;
   PSB_LAUNCH_CHECK("attention_prefill_tcgen05");
   return 0;

@@ -140,6 +140,17 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// A sink joins a finished softmax: one more term in the denominator, with a score of its own and no value.  ``e`` is
+// the exponent the row's sum ``l`` and its accumulated values refer to (l = sum of 2^(x - e)) and ``s`` the sink's score,
+// both in powers of two (natural scores times log2 e); -inf for a row that saw no key.  Returns what the accumulated
+// values are multiplied by in place of 1 / l.  The larger of e and s is taken out first, so neither term overflows.
+__device__ __forceinline__ float sink_quotient2(float e, float l, float s) {
+  const float top = fmaxf(e, s);
+  const float a = exp2f(e - top);  // 0 from -inf
+  return a / fmaf(l, a, exp2f(s - top));
+}
+constexpr float PSB_LOG2E = 1.4426950408889634f;
+
 // Calls f.template operator()<T>() with T chosen by a PsbDtype code.
 #define PSB_DISPATCH_DTYPE(code, T, ...)                       \
   if ((code) == PSB_F32) { using T = float; __VA_ARGS__ }      \

@@ -274,7 +274,7 @@ def qkv_rope_append(x: NormedRows, w_qkv: torch.Tensor, positions: torch.Tensor,
 
 
 def attention_generic(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
-                      token_item: torch.Tensor, *, window: int | None, scale: float) -> torch.Tensor:
+                      token_item: torch.Tensor, *, window: int | None, scale: float, sink: torch.Tensor | None = None) -> torch.Tensor:
     _dev(q, "queries"), _dev(kv, "cache entry")
     _i32(table, "page table"), _i32(positions, "positions"), _i32(token_item, "token-to-item map")
     t, hq, d = q.shape
@@ -284,15 +284,18 @@ def attention_generic(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, po
     out = torch.empty((t, hq * d), dtype=q.dtype, device=q.device)
     check(lib().psb_attention_generic(q.data_ptr(), _code(q, "queries"), kv.data_ptr(), _code(kv, "cache entry"),
                                       table.data_ptr(), table.shape[1], positions.data_ptr(), token_item.data_ptr(),
-                                      out.data_ptr(), t, hq, hkv, d, page, int(window or 0), float(scale), _stream()),
+                                      out.data_ptr(), t, hq, hkv, d, page, int(window or 0), float(scale), _ptr(sink), _stream()),
           "attention")
     return out
 
 
 def attention(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
               token_item: torch.Tensor, *, window: int | None = None, scale: float | None = None,
-              ctx=None) -> torch.Tensor:
-    """Causal grouped-query attention of the step's tokens over their requests' pages -> [T, hq*D]."""
+              ctx=None, sink: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal grouped-query attention of the step's tokens over their requests' pages -> [T, hq*D].  ``sink`` (float32
+    [hq]): a score per head that joins every row's softmax denominator without a key or a value."""
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != q.shape[1] or not sink.is_cuda or not sink.is_contiguous()):
+        raise KernelError(f"sinks must be float32 [{q.shape[1]}] on the device")
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     if q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and ctx is not None:
@@ -303,10 +306,10 @@ def attention(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, positions:
         extras = getattr(ctx, "extras", None)
         fast = attention_bf16(q, kv, table, ctx.item_start, ctx.kv_len, None, None, window=window, scale=scale,
                               static_kv_len=extras.get("static_kv_len") if extras is not None else None,
-                              plans=extras, items=ctx.items, token_item=_i32(token_item, "token-to-item map"))
+                              plans=extras, items=ctx.items, token_item=_i32(token_item, "token-to-item map"), sink=sink)
         if fast is not None:
             return fast
-    return attention_generic(q, kv, table, positions, token_item, window=window, scale=scale)
+    return attention_generic(q, kv, table, positions, token_item, window=window, scale=scale, sink=sink)
 
 
 def act_mul(gate_up: torch.Tensor, activation: str = "silu") -> torch.Tensor:
@@ -1006,19 +1009,24 @@ def normed_pair_sum(a: torch.Tensor, b: torch.Tensor, gain_a: torch.Tensor, gain
 def attention_prepare(proj: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,
                       dim: int, vdim: int, page_size: int, cos: torch.Tensor | None = None, sin: torch.Tensor | None = None,
                       rotary_dim: int | None = None, interleaved: bool = False, unit_norm_eps: float | None = None,
-                      head_factor: torch.Tensor | None = None, values_are_keys: bool = False) -> torch.Tensor:
+                      head_factor: torch.Tensor | None = None, values_are_keys: bool = False,
+                      split_planes: bool = False) -> torch.Tensor:
     """One pass over the fused projection [T, q | k | v] (or [T, q | k] with ``values_are_keys``): optional rotation of
     the first ``rotary_dim`` elements of query and key heads by position (``cos``/``sin`` float32 [positions,
     rotary_dim/2]), optional division of every query and key head by its root mean square (``unit_norm_eps``), an
     optional float32 factor per query head; keys and values appended to the cache entry [pages, 1, hkv, page_size,
-    dim + vdim].  Returns the queries [T, hq, dim]."""
+    dim + vdim], or with ``split_planes`` (vdim == dim) [pages, 2, hkv, page_size, dim]: keys in plane 0, values in
+    plane 1.  Returns the queries [T, hq, dim]."""
     _dev(kv, "cache entry"), _i32(table, "page table")
     t = proj.shape[0]
     want = num_heads * dim + num_kv_heads * dim + (0 if values_are_keys else num_kv_heads * vdim)
     if not proj.is_cuda or proj.dim() != 2 or proj.shape[1] != want or proj.stride(1) != 1:
         raise KernelError(f"projection output must be [T, {want}] on the device (rows may be part of wider ones), is {tuple(proj.shape)}")
-    if kv.dim() != 5 or tuple(kv.shape[1:]) != (1, num_kv_heads, page_size, dim + vdim):
-        raise KernelError(f"cache entry must be [pages, 1, {num_kv_heads}, {page_size}, {dim + vdim}], is {tuple(kv.shape)}")
+    entry = (2, num_kv_heads, page_size, dim) if split_planes else (1, num_kv_heads, page_size, dim + vdim)
+    if kv.dim() != 5 or tuple(kv.shape[1:]) != entry or not kv.is_contiguous():
+        raise KernelError(f"cache entry must be [pages, {', '.join(map(str, entry))}], is {tuple(kv.shape)}")
+    if split_planes and vdim != dim:
+        raise KernelError(f"keys and values in planes of their own need vdim == dim, not {vdim} and {dim}")
     if values_are_keys and vdim != dim:
         raise KernelError(f"keys that serve as values need vdim == dim, not {vdim} and {dim}")
     max_pos = 0
@@ -1039,7 +1047,7 @@ def attention_prepare(proj: torch.Tensor, kv: torch.Tensor, table: torch.Tensor,
                                       _ptr(cos), _ptr(sin), _ptr(head_factor), kv.data_ptr(), _code(kv, "cache entry"), q.data_ptr(),
                                       t, num_heads, num_kv_heads, dim, vdim, page_size, kv.shape[0], max_pos, rotary_dim,
                                       1 if interleaved else 0, -1.0 if unit_norm_eps is None else float(unit_norm_eps),
-                                      1 if values_are_keys else 0, _stream()), "attention_prepare")
+                                      1 if values_are_keys else 0, 1 if split_planes else 0, _stream()), "attention_prepare")
     return q
 
 

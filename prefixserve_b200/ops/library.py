@@ -39,15 +39,15 @@ _SIGNATURES: dict[str, list] = {
     #  hq, hkv, D, page_size, num_pages, max_positions, stream)
     "psb_gemm_stream_norm_rope": [P, P, P, P, P, I, I, F, I, P, P, P, I, P, P, P, P, I, I, I, I, I, I, P],
     # (q, dtype, kv, kv_dtype, table, table_width, positions, token_item, out, T, hq, hkv, D, page_size, window,
-    #  scale, stream)
-    "psb_attention_generic": [P, I, P, I, P, I, P, P, P, I, I, I, I, I, I, F, P],
+    #  scale, sink, stream)
+    "psb_attention_generic": [P, I, P, I, P, I, P, P, P, I, I, I, I, I, I, F, P, P],
     # (gate_up, dtype, out, T, I, activation, stream)
     "psb_silu_mul": [P, I, P, I, I, I, P],
     # (h, delta, delta_dtype, total, stream)
     "psb_residual_add": [P, P, I, L, P],
     # (q, kv, table, table_width, item_start, kv_len, out, num_items, num_tiles, hq, hkv, D, page_size, window, scale,
-    #  skip_single, stream)
-    "psb_attention_prefill_bf16": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P],
+    #  skip_single, sink, stream)
+    "psb_attention_prefill_bf16": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P, P],
     # (D) -> rows per CTA
     "psb_attention_prefill_rows_per_cta": [I],
     # (D, page_size) -> 1 if the tcgen05 prefill attention takes them
@@ -55,21 +55,21 @@ _SIGNATURES: dict[str, list] = {
     # () -> rows per CTA
     "psb_attention_prefill_tcgen05_rows_per_cta": [],
     # (q, kv, table, table_width, item_start, kv_len, out, num_items, num_pairs, T, hq, hkv, D, page_size, num_pages,
-    #  window, scale, skip_single, rows_per_cta, kv_splits, part_o, part_ml, token_item, stream)
-    "psb_attention_prefill_tcgen05": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, L, I, F, I, I, I, P, P, P, P],
+    #  window, scale, skip_single, rows_per_cta, kv_splits, part_o, part_ml, token_item, sink, stream)
+    "psb_attention_prefill_tcgen05": [P, P, P, I, P, P, P, I, I, I, I, I, I, I, L, I, F, I, I, I, P, P, P, P, P],
     # () -> 0 while no bounded wait of the tcgen05 attention kernel has ever run out
     "psb_attention_tcgen05_status": [],
     # (q, kv, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, D, page_size, window,
-    #  scale, chunk, max_splits, all_single, stream)
-    "psb_attention_decode_bf16": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P],
+    #  scale, chunk, max_splits, all_single, sink, stream)
+    "psb_attention_decode_bf16": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P],
     # (hq, hkv, D, page_size) -> 1 if the TMA-fed decode attention takes the shape
     "psb_attention_decode_tma_supported": [I, I, I, I],
     # (q, kv, table, table_width, item_start, kv_len, out, part_o, part_ml, num_items, hq, hkv, D, page_size, num_pages,
-    #  window, scale, chunk, max_splits, all_single, stream)
-    "psb_attention_decode_tma_bf16": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, L, I, F, I, I, I, P],
+    #  window, scale, chunk, max_splits, all_single, sink, stream)
+    "psb_attention_decode_tma_bf16": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, L, I, F, I, I, I, P, P],
     "psb_attention_decode_tma_status": [],
-    # (part_o, part_ml, item_start, kv_len, out, num_items, hq, D, window, chunk, max_splits, all_single, stream)
-    "psb_attention_decode_merge_bf16": [P, P, P, P, P, I, I, I, I, I, I, I, P],
+    # (part_o, part_ml, item_start, kv_len, out, num_items, hq, D, window, chunk, max_splits, all_single, sink, stream)
+    "psb_attention_decode_merge_bf16": [P, P, P, P, P, I, I, I, I, I, I, I, P, P],
     # (x, W, y, out_dtype, M, N, K, sms, stream)
     "psb_gemm_stream": [P, P, P, I, I, I, I, I, P],
     # (x, W, act, M, I, K, sms, activation, stream)
@@ -194,8 +194,8 @@ _SIGNATURES: dict[str, list] = {
     # (a, b, dtype, gain_a, gain_b, out_f32, T, W, eps, weight, stream)
     "psb_normed_pair_sum": [P, P, I, P, P, P, I, I, F, F, P],
     # (proj, ld, dtype, positions, token_item, table, table_width, cos, sin, head_factor, kv, kv_dtype, q_out, T, hq, hkv, dim, vdim,
-    #  page_size, num_pages, max_positions, rotary_dim, interleaved, eps, values_are_keys, stream)
-    "psb_attention_prepare": [P, L, I, P, P, P, I, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, I, F, I, P],
+    #  page_size, num_pages, max_positions, rotary_dim, interleaved, eps, values_are_keys, split_planes, stream)
+    "psb_attention_prepare": [P, L, I, P, P, P, I, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P],
     # (proj, ld, dtype, bias_z, bias_x, state, stride, item_start, slots, carry, start, out, items, T, W, num_slots, chunk,
     #  two_pass, stream)
     "psb_min_gru": [P, L, I, P, P, P, L, P, P, P, P, P, I, I, I, I, I, I, P],

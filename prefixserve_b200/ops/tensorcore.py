@@ -449,10 +449,11 @@ def _attention_plan(new_tokens: Sequence[int], kv_lens: Sequence[int], window: i
 def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_start: torch.Tensor, kv_len: torch.Tensor,
                    new_tokens: Sequence[int] | None, kv_lens: Sequence[int] | None, *, window: int | None, scale: float,
                    static_kv_len: int | None = None, plans: dict | None = None, items=None,
-                   token_item: torch.Tensor | None = None) -> torch.Tensor | None:
+                   token_item: torch.Tensor | None = None, sink: torch.Tensor | None = None) -> torch.Tensor | None:
     """Tensor-core attention for a step.  ``new_tokens``/``kv_lens`` are the host copies of what ``item_start`` and
     ``kv_len`` hold on the device (or ``items`` with ``.start``/``.end``, read only when no plan is cached yet).
-    Returns None when no kernel here takes the shape (the caller falls back).  ``plans``: a dict that lives as long as
+    Returns None when no kernel here takes the shape (the caller falls back).  ``sink`` (float32 [hq] on the device): a
+    score per head that joins every row's softmax denominator without a value.  ``plans``: a dict that lives as long as
     the step; layers with the same shape reuse the launch plan the first of them worked out.
 
     With ``static_kv_len`` (a step that is being captured for replay) the launch shapes are derived from that
@@ -474,6 +475,7 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
     out = torch.empty((t, hq * d), dtype=torch.bfloat16, device=q.device)
     stream = stream_handle()
     b = plan["b"]
+    sk = sink.data_ptr() if sink is not None else None
     if plan["use_decode"]:
         chunk, max_splits = plan["chunk"], plan["max_splits"]
         part_o = part_ml = None
@@ -487,16 +489,16 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
             check(lib().psb_attention_decode_tma_bf16(
                 q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
                 out.data_ptr(), po, pm, b, hq, hkv, d, page, kv.shape[0], w, float(scale), chunk, max_splits,
-                plan["all_single"], stream), "attention_decode")
+                plan["all_single"], None if max_splits > 1 else sk, stream), "attention_decode")
             launch_counts["attention_decode_tma"] += 1  # the same step of the model, by which kernel
             if max_splits > 1:
                 check(lib().psb_attention_decode_merge_bf16(po, pm, item_start.data_ptr(), kv_len.data_ptr(), out.data_ptr(), b, hq, d,
-                                                            w, chunk, max_splits, plan["all_single"], stream), "attention_merge")
+                                                            w, chunk, max_splits, plan["all_single"], sk, stream), "attention_merge")
         else:
             check(lib().psb_attention_decode_bf16(
                 q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
                 out.data_ptr(), po, pm, b, hq, hkv, d, page, w, float(scale), chunk, max_splits,
-                plan["all_single"], stream), "attention_decode")
+                plan["all_single"], sk, stream), "attention_decode")
     if plan["tcgen05"] and q.is_contiguous() and kv.is_contiguous():
         splits = plan["kv_splits"] if token_item is not None else 1
         po = pm = None
@@ -507,7 +509,7 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
             q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
             out.data_ptr(), b, plan["pairs"], t, hq, hkv, d, page, kv.shape[0], w, float(scale),
             1 if plan["use_decode"] else 0, plan["rows_per_cta"], splits, po, pm,
-            token_item.data_ptr() if token_item is not None else None, stream), "attention_prefill_tcgen05")
+            token_item.data_ptr() if token_item is not None else None, sk, stream), "attention_prefill_tcgen05")
         return out
     tiles = plan.get("tiles")
     if tiles is None:  # planned for the tcgen05 kernel, which these tensors' layout rules out
@@ -517,5 +519,5 @@ def attention_bf16(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, item_
     if tiles:
         check(lib().psb_attention_prefill_bf16(
             q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], item_start.data_ptr(), kv_len.data_ptr(),
-            out.data_ptr(), b, tiles, hq, hkv, d, page, w, float(scale), 1 if plan["use_decode"] else 0, stream), "attention_prefill")
+            out.data_ptr(), b, tiles, hq, hkv, d, page, w, float(scale), 1 if plan["use_decode"] else 0, sk, stream), "attention_prefill")
     return out

@@ -11,8 +11,13 @@ q, k (and v) come from one fused projection without biases; per head and in floa
 
 Query head h reads key/value head h // (heads / kv_heads).  ``values``: "projected" (a projection of their own, size
 ``vdim``) or "keys" (the projected key, before rotation and norm, is also the value; no v_proj).  Optional ``window``
-and ``chunk`` masks as in ``biased_attention``, whose cache layout (one row per token and key/value head: key, then
-value) and attention kernels this part shares; only the pass between projection and scores is its own.
+and ``chunk`` masks.
+
+Only the pass between projection and scores is this part's own; the attention kernels are those of the other
+attention parts.  With keys and values of one size that the tensor-core kernels take (64 or 128) and no chunk mask,
+the cache entry has a plane of keys and a plane of values and ``ops.attention`` reads it (the kernels of the plain
+``attention`` part, which take the sink at the end of a row's sum); any other sizes, or a chunk mask, keep one row per
+token and key/value head (key, then value) and the kernels of ``biased_attention``.
 """
 
 from __future__ import annotations
@@ -25,6 +30,9 @@ from .. import ops
 from ..config.spec import PartSpec
 from .base import CacheNeed, CacheView, Mixer, PagedKV, ParamSpec, StepContext
 from .registry import make, register_mixer
+
+
+SPLIT_PLANE_SIZES = (64, 128)  # head sizes of the kernels behind ``ops.attention``
 
 
 class UnitNormAttention(Mixer):
@@ -51,6 +59,7 @@ class UnitNormAttention(Mixer):
         self.position = make("position", params.get("position") or PartSpec("none"))
         self.rotary_dim = int(getattr(self.position, "rotary_dim", None) or self.dim)
         self.interleaved = getattr(self.position, "layout", "half") == "interleaved"
+        self.split_planes = self.chunk is None and self.vdim == self.dim and self.dim in SPLIT_PLANE_SIZES
         self.w_in = self.w_o = self.temperature = self.sink = None
 
     def param_specs(self):
@@ -63,6 +72,8 @@ class UnitNormAttention(Mixer):
         return specs
 
     def cache_need(self):
+        if self.split_planes:
+            return CacheNeed(paged=PagedKV(self.hkv, self.dim, self.window, "natural"))
         return CacheNeed(paged=PagedKV(self.hkv, self.dim + self.vdim, self.window, "natural", planes=1, chunk=self.chunk))
 
     def load(self, tensors, *, compute_dtype, device):
@@ -90,7 +101,12 @@ class UnitNormAttention(Mixer):
         q = ops.attention_prepare(proj, cache.kv, table, ctx, num_heads=self.hq, num_kv_heads=self.hkv, dim=self.dim,
                                   vdim=self.vdim, page_size=cache.page_size, cos=self.position.cos, sin=self.position.sin,
                                   rotary_dim=self.rotary_dim, interleaved=self.interleaved, unit_norm_eps=self.eps,
-                                  head_factor=self.temperature, values_are_keys=self.values == "keys")
+                                  head_factor=self.temperature, values_are_keys=self.values == "keys",
+                                  split_planes=self.split_planes)
+        if self.split_planes:
+            o = ops.attention(q, cache.kv, table, ctx.positions, ctx.token_item, window=self.window, scale=self.scale, ctx=ctx,
+                              sink=self.sink)
+            return ops.last_product(o, self.w_o, ctx)
         o = ops.attention_over_rows(q, cache.kv, table, ctx, num_heads=self.hq, num_kv_heads=self.hkv, dim=self.dim,
                                     vdim=self.vdim, page_size=cache.page_size, scale=self.scale, window=self.window,
                                     chunk=self.chunk, sink=self.sink)

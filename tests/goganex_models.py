@@ -76,6 +76,14 @@ CONFIGS = {
         layer("parallel", parallel(heads=4, kv_heads=1, dim=32, scale=0.08, width=96), dense(256, limit=2.5)),
         layer("attention", attention(heads=8, kv_heads=8, dim=16, vdim=40, scale=0.12, rotation=rot(16)), None),
     ], vocab=512, width=128, scale=3.5, loop=(0, 2, 2)),
+    # keys and values of one size, 64 or 128: the cache entry with a plane of keys and a plane of values, and the
+    # attention kernels that the plain attention part uses (here with the sink, the factors and keys that are values)
+    "planes": config([
+        layer("attention", attention(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.06, rotation=rot(32, scaling=SCALED)), dense(160, limit=1.5)),
+        layer("parallel", parallel(heads=2, kv_heads=1, dim=128, scale=0.05, width=72), None),
+        layer("attention", attention(heads=3, kv_heads=3, dim=128, vdim=128, scale=0.04, rotation=rot(128, base=5000.0)), dense(96, limit=2.0)),
+        layer("parallel", parallel(heads=6, kv_heads=2, dim=64, scale=0.07, width=40), dense(128, limit=1.0)),
+    ], vocab=300, width=96, eps=1e-5, scale=3.0, loop=(1, 3, 2)),
 }
 
 

@@ -136,19 +136,20 @@ def test_captured_steps_give_what_uncaptured_ones_give(made):
 MARK, ASK = 62, 63
 
 
-def echo_model(kind, dtype):
+def echo_model(kind, dtype, dim=16):
     """One layer whose attention answers the token ASK with the key of the token MARK, wherever that lies: the key
     matrix is the first query head's behind a fixed permutation of the width, and ASK's embedding is MARK's under the
     same permutation, so ASK's query is MARK's key (up to the few rotated elements and a weak token shift) and its
-    score stands out among hundreds of random ones.  Whoever loses that one key gives a visibly different row."""
+    score stands out among hundreds of random ones.  Whoever loses that one key gives a visibly different row.  The
+    scale goes down as the head grows, so that the one score stands as high above the others whatever the size."""
     if kind == "attention":
-        mixer, p = gm.attention(heads=2, kv_heads=1, dim=16, vdim=8, scale=0.8, rotation=gm.rot(4, base=100.0)), "l0.mix."
+        mixer, p = gm.attention(heads=2, kv_heads=1, dim=dim, vdim=8 if dim == 16 else dim, scale=12.8 / dim, rotation=gm.rot(4, base=100.0)), "l0.mix."
     else:
-        mixer, p = gm.parallel(heads=2, kv_heads=1, dim=16, scale=1.1, width=8), "l0.mix.left."
+        mixer, p = gm.parallel(heads=2, kv_heads=1, dim=dim, scale=17.6 / dim, width=8), "l0.mix.left."
     cfg = gm.config([gm.layer(kind, mixer, None)], vocab=64, width=32)
     w = gm.tensors(cfg, seed=11)
     turn = torch.eye(32)[torch.roll(torch.arange(32), 1)]
-    w[p + "k"] = w[p + "q"][:16] @ turn
+    w[p + "k"] = w[p + "q"][:dim] @ turn
     w["embed"][ASK] = turn @ w["embed"][MARK]
     w["l0.norm1"] = torch.ones(32)
     w["l0.shift"] *= 0.05
@@ -160,10 +161,12 @@ def echo_model(kind, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("marked", [0, 3, 63, 64])
 @pytest.mark.parametrize("kind", ["attention", "parallel"])
-def test_one_key_far_back_or_at_a_page_border_is_found(tmp_path, kind, dtype, marked):
+@pytest.mark.parametrize("dim", [16, 64])
+def test_one_key_far_back_or_at_a_page_border_is_found(tmp_path, dim, kind, dtype, marked):
     """The marked key is a sequence's first, an early one, a page's last or a page's first (pages of 16 and of 64);
-    it is asked for right behind it and hundreds of tokens later, in prompts, in portions and in single tokens."""
-    cfg, held, exact = echo_model(kind, dtype)
+    it is asked for right behind it and hundreds of tokens later, in prompts, in portions and in single tokens.  Heads
+    of 16: the cache entry with a row per token; of 64: planes of keys and values and the kernels that read those."""
+    cfg, held, exact = echo_model(kind, dtype, dim)
     folder = gm.write_folder(tmp_path / "m", cfg, held)
     n = 330
     toks = helpers.random_tokens(62, n, seed=5)
@@ -231,9 +234,11 @@ def step_context(lengths, starts, slots):
         positions += list(range(s, s + n))
         item_of += [i] * n
         offsets.append(offsets[-1] + n)
+    items = [types.SimpleNamespace(slot=sl, start=s, end=s + n, first_token=o) for sl, s, n, o in zip(slots, starts, lengths, offsets)]
     return types.SimpleNamespace(positions=dev(positions), token_item=dev(item_of), item_start=dev(offsets), slots=dev(slots),
                                  num_items=len(lengths), num_tokens=len(positions), max_new_tokens=max(lengths),
-                                 max_kv_len=max(n + s for n, s in zip(lengths, starts)), extras={}, items=None)
+                                 kv_len=dev([n + s for n, s in zip(lengths, starts)]),
+                                 max_kv_len=max(n + s for n, s in zip(lengths, starts)), extras={}, items=items)
 
 
 def test_scaled_embedding_alone():
@@ -303,11 +308,11 @@ def test_min_gru_alone(dtype, lengths):
     assert torch.equal(state[:, :7].cpu(), before[:, :7]) and torch.equal(state[len(lengths)].cpu(), before[len(lengths)])
 
 
-def paged_entry(hkv, row, page_size, tokens_per_item, dtype, seed=0):
+def paged_entry(hkv, row, page_size, tokens_per_item, dtype, seed=0, planes=1):
     """A pool of pages in shuffled order, filled with NaN, and each item's table."""
     per = [-(-n // page_size) for n in tokens_per_item]
     order = torch.randperm(sum(per) + 3, generator=torch.Generator().manual_seed(seed)).tolist()
-    kv = torch.full((sum(per) + 3, 1, hkv, page_size, row), float("nan"), dtype=dtype).cuda()
+    kv = torch.full((sum(per) + 3, planes, hkv, page_size, row), float("nan"), dtype=dtype).cuda()
     table = torch.full((len(per), max(per)), -1, dtype=torch.int32)
     for i, n in enumerate(per):
         table[i, :n] = torch.tensor([order.pop() for _ in range(n)], dtype=torch.int32)
@@ -321,19 +326,32 @@ ATTENTION_SHAPES = [
     (6, 1, 12, 5, None, False, True, True, True, False),
     (2, 1, 32, 32, 16, False, False, False, True, False),
     (8, 4, 64, 64, 32, True, True, True, True, False),     # sizes the tensor-core kernel takes
+    (4, 1, 128, 128, 64, True, True, True, True, False),
+    (4, 2, 64, 64, None, False, True, False, False, True),
+    (2, 2, 128, 128, 128, False, False, True, True, False),  # a rotation of halves: the general pass in front
 ]
+# (tokens already there, new tokens) per request: single tokens beside short and long portions; a long portion alone (the
+# kernels that cut a portion's keys into ranges); single tokens only, far enough back for several key ranges
+ATTENTION_STEPS = [([37, 0, 9], [1, 2, 70]), ([150], [300]), ([700, 3, 1100], [1, 1, 1])]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("planes", [1, 2])
+@pytest.mark.parametrize("steps", range(len(ATTENTION_STEPS)))
 @pytest.mark.parametrize("shape", ATTENTION_SHAPES)
-def test_prepared_attention_alone(shape, dtype):
-    """Two steps over three requests: their first tokens, then portions of 1, 2 and 70 tokens behind them; pages of 8 in
-    shuffled order.  Against the plain rotation, unit norm and softmax with factors and a sink."""
+def test_prepared_attention_alone(shape, steps, planes, dtype):
+    """Two steps over the requests: their first tokens, then the new ones behind them; pages in shuffled order.  Against
+    the plain rotation, unit norm and softmax with factors and a sink.  ``planes`` 1: a row per token (key, then value)
+    and the kernels that read such rows; 2: a plane of keys and a plane of values and the kernels of ``ops.attention``."""
     from prefixserve_b200 import ops
     hq, hkv, dim, vdim, rotated, interleaved, unit, factors, sink, keys = shape
-    eps, scale, page = 1e-5, 0.37, 8
+    if planes == 2 and dim != vdim:
+        pytest.skip("planes of their own need keys and values of one size")
+    if steps and (dim < 64 or planes == 1):
+        pytest.skip("the long steps are for the kernels that cut keys into ranges")
+    eps, scale, page = 1e-5, 0.37 if dim < 64 else 0.11, 8 if planes == 1 else 16
     g = torch.Generator().manual_seed(hq)
-    had, new = [37, 0, 9], [1, 2, 70]
+    had, new = ATTENTION_STEPS[steps]
     total = [a + b for a, b in zip(had, new)]
     width = (hq + hkv) * dim + (0 if keys else hkv * vdim)
     seqs = [torch.randn(n, width, generator=g).to(dtype) for n in total]
@@ -341,9 +359,9 @@ def test_prepared_attention_alone(shape, dtype):
     rot = None if rotated is None else gm.rot(rotated, base=300.0, scaling=(4.0, 1.0, 4.0, 32))
     cos = sin = None
     if rot is not None:
-        angle = torch.arange(128, dtype=torch.float64)[:, None] * plain.rotary_frequencies(rot)[None, :]
+        angle = torch.arange(max(total) + 1, dtype=torch.float64)[:, None] * plain.rotary_frequencies(rot)[None, :]
         cos, sin = torch.cos(angle).float().cuda(), torch.sin(angle).float().cuda()
-    kv, table = paged_entry(hkv, dim + vdim, page, total, dtype)
+    kv, table = paged_entry(hkv, dim + vdim if planes == 1 else dim, page, total, dtype, planes=planes)
     outs = {}
     for step, (lengths, starts) in enumerate((([h for h in had if h], [0 for h in had if h]), (new, had))):
         items = [i for i, h in enumerate(had) if h] if step == 0 else [0, 1, 2]
@@ -352,9 +370,14 @@ def test_prepared_attention_alone(shape, dtype):
         tab = table[items].contiguous()
         q = ops.attention_prepare(rows, kv, tab, ctx, num_heads=hq, num_kv_heads=hkv, dim=dim, vdim=vdim, page_size=page,
                                   cos=cos, sin=sin, rotary_dim=rotated, interleaved=interleaved, unit_norm_eps=eps if unit else None,
-                                  head_factor=None if temp is None else temp.cuda(), values_are_keys=keys)
-        o = ops.attention_over_rows(q, kv, tab, ctx, num_heads=hq, num_kv_heads=hkv, dim=dim, vdim=vdim, page_size=page,
-                                    scale=scale, sink=torch.zeros(hq).cuda() if sink else None)
+                                  head_factor=None if temp is None else temp.cuda(), values_are_keys=keys,
+                                  split_planes=planes == 2)
+        if planes == 2:
+            o = ops.attention(q, kv, tab, ctx.positions, ctx.token_item, scale=scale, ctx=ctx,
+                              sink=torch.zeros(hq).cuda() if sink else None)
+        else:
+            o = ops.attention_over_rows(q, kv, tab, ctx, num_heads=hq, num_kv_heads=hkv, dim=dim, vdim=vdim, page_size=page,
+                                        scale=scale, sink=torch.zeros(hq).cuda() if sink else None)
         at = 0
         for i, n, s in zip(items, lengths, starts):
             outs[i, step] = (s, o[at: at + n].cpu().double())

@@ -26,7 +26,7 @@ def _library():
     from prefixserve_b200.build import ensure_kernels
     lib = ctypes.CDLL(str(ensure_kernels()))
     P, I, F = c_void_p, c_int, c_float
-    lib.psb_attention_decode_bf16.argtypes = [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P]
+    lib.psb_attention_decode_bf16.argtypes = [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P]
     lib.psb_attention_decode_bf16.restype = c_int
     lib.psb_attention_decode_bf16_static.argtypes = [P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, I, P]
     lib.psb_attention_decode_bf16_static.restype = c_int
@@ -62,7 +62,7 @@ def _run(lib, pr, chunk, static):
         n = pr["b"] * pr["hq"] * max_splits
         part_o = torch.empty(n * pr["d"], dtype=torch.float32, device=DEV)
         part_ml = torch.empty(n * 2, dtype=torch.float32, device=DEV)
-        rc = lib.psb_attention_decode_bf16(*head, part_o.data_ptr(), part_ml.data_ptr(), *common_tail)
+        rc = lib.psb_attention_decode_bf16(*head, part_o.data_ptr(), part_ml.data_ptr(), *common_tail[:-1], None, stream)  # no sink
     assert rc == 0, lib.psb_last_error().decode()
     torch.cuda.synchronize()
     return out
