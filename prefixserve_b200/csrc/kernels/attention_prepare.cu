@@ -14,7 +14,7 @@
 //
 // Two kernels.  The general one: one block per token, a warp per head in turn; the head lies in the warp's
 // shared-memory row between the steps.  The other, for heads of 64, 128 or 256 elements whose rotation (if any) pairs
-// neighbours: a warp per (token, head), the head in registers (every lane a run of dim/32 elements, which holds whole
+// neighbours: a warp per (token, head) or per (token, four heads), the head in registers (every lane a run of dim/32 elements, which holds whole
 // pairs), one wide load and one wide store per lane and row.
 // Rotation, statistics and factors are float32; storage is float32 or bfloat16.
 #include "common.cuh"
@@ -93,8 +93,10 @@ struct alignas(sizeof(T) * N) Run {
   T v[N];
 };
 
-// grid: T * ceil((hq + hkv) / PREP_WARPS) blocks; warp w of block b: token b / groups, head (b % groups) * PREP_WARPS + w.
-template <typename T, typename TKV, int DIM>
+// grid: T * groups blocks, groups = ceil((hq + hkv) / (PREP_WARPS * HPW)); warp w of block b: token b / groups, heads
+// ((b % groups) * PREP_WARPS + w) * HPW .. + HPW - 1.  HPW > 1 (long steps): the rows of a warp's heads are asked for
+// together, before any of them is used, so that a lane has several loads in flight.
+template <typename T, typename TKV, int DIM, int HPW>
 __global__ void __launch_bounds__(PREP_WARPS * 32)
 attention_prepare_rows_kernel(const T* __restrict__ proj, long long ld, const int32_t* __restrict__ positions,
                               const int32_t* __restrict__ token_item, const int32_t* __restrict__ table, int table_width,
@@ -105,71 +107,88 @@ attention_prepare_rows_kernel(const T* __restrict__ proj, long long ld, const in
   constexpr int N = DIM / 32;
   pdl_trigger();
   const int t = blockIdx.x / groups;
-  const int head = (blockIdx.x - t * groups) * PREP_WARPS + (threadIdx.x >> 5);
+  const int head0 = ((blockIdx.x - t * groups) * PREP_WARPS + (threadIdx.x >> 5)) * HPW;
   const int lane = threadIdx.x & 31;
   // positions and tables are inputs of the step: they may be read before the preceding kernel has finished
   const int p = positions[t];
   const int page = table[(size_t)token_item[t] * table_width + p / page_size];
   pdl_wait();
-  if (head >= hq + hkv) return;
-  const bool is_q = head < hq;
+  const int heads = hq + hkv;
+  if (head0 >= heads) return;
   const T* row = proj + (size_t)t * ld;
-  const T* src = row + (size_t)head * DIM;
-  const Run<T, N> raw = *reinterpret_cast<const Run<T, N>*>(src + lane * N);
-  float x[N];
+  Run<T, N> raw[HPW], vin[HPW];
 #pragma unroll
-  for (int i = 0; i < N; ++i) x[i] = to_float<T>(raw.v[i]);
-  if (cos_t != nullptr && p >= 0 && p < max_positions) {
-    const float* cs = cos_t + (size_t)p * (rotary_dim / 2);
-    const float* sn = sin_t + (size_t)p * (rotary_dim / 2);
+  for (int i = 0; i < HPW; ++i) {
+    const int head = head0 + i;
+    if (head < heads) raw[i] = *reinterpret_cast<const Run<T, N>*>(row + (size_t)head * DIM + lane * N);
+    if (head < heads && head >= hq && !values_are_keys)
+      vin[i] = *reinterpret_cast<const Run<T, N>*>(row + (size_t)heads * DIM + (size_t)(head - hq) * DIM + lane * N);
+  }
+  const bool turn = cos_t != nullptr && p >= 0 && p < max_positions;
+  float cs[N / 2], sn[N / 2];
+  if (turn) {
 #pragma unroll
     for (int i = 0; i < N; i += 2) {
       const int d = lane * N + i;  // even: the pair (d, d + 1) turns by angle d / 2
-      if (d < rotary_dim) {
-        float o1, o2;
-        rotate_pair(x[i], x[i + 1], cs[d >> 1], sn[d >> 1], o1, o2);
-        x[i] = o1;
-        x[i + 1] = o2;
-      }
+      cs[i / 2] = d < rotary_dim ? cos_t[(size_t)p * (rotary_dim / 2) + (d >> 1)] : 1.f;
+      sn[i / 2] = d < rotary_dim ? sin_t[(size_t)p * (rotary_dim / 2) + (d >> 1)] : 0.f;
     }
   }
-  float factor = 1.f;
-  if (eps >= 0.f) {
-    float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < N; ++i) ss = fmaf(x[i], x[i], ss);
-    factor = 1.f / sqrtf(warp_sum(ss) / (float)DIM + eps);
+  for (int hh = 0; hh < HPW; ++hh) {
+    const int head = head0 + hh;
+    if (head >= heads) break;
+    float x[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) x[i] = to_float<T>(raw[hh].v[i]);
+    if (turn) {
+#pragma unroll
+      for (int i = 0; i < N; i += 2) {
+        if (lane * N + i < rotary_dim) {
+          float o1, o2;
+          rotate_pair(x[i], x[i + 1], cs[i / 2], sn[i / 2], o1, o2);
+          x[i] = o1;
+          x[i + 1] = o2;
+        }
+      }
+    }
+    float factor = 1.f;
+    if (eps >= 0.f) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < N; ++i) ss = fmaf(x[i], x[i], ss);
+      factor = 1.f / sqrtf(warp_sum(ss) / (float)DIM + eps);
+    }
+    if (head < hq) {
+      const float f = head_factor ? head_factor[head] : 1.f;
+      Run<T, N> o;
+#pragma unroll
+      for (int i = 0; i < N; ++i) o.v[i] = from_float<T>(x[i] * factor * f);
+      *reinterpret_cast<Run<T, N>*>(q_out + ((size_t)t * hq + head) * DIM + lane * N) = o;
+      continue;
+    }
+    if (page < 0 || page >= num_pages) continue;  // tables are checked on the host; never write outside the pool
+    const int g = head - hq;
+    const size_t slot = (size_t)(p % page_size);
+    TKV* dst = split_planes ? kv + ((((size_t)page * 2) * hkv + g) * page_size + slot) * DIM
+                            : kv + (((size_t)page * hkv + g) * page_size + slot) * (2 * DIM);
+    TKV* vdst = split_planes ? dst + (size_t)hkv * page_size * DIM : dst + DIM;
+    Run<TKV, N> k;
+#pragma unroll
+    for (int i = 0; i < N; ++i) k.v[i] = from_float<TKV>(x[i] * factor);
+    *reinterpret_cast<Run<TKV, N>*>(dst + lane * N) = k;
+    const Run<T, N> vsrc = values_are_keys ? raw[hh] : vin[hh];
+    Run<TKV, N> v;
+#pragma unroll
+    for (int i = 0; i < N; ++i) v.v[i] = from_float<TKV>(to_float<T>(vsrc.v[i]));
+    *reinterpret_cast<Run<TKV, N>*>(vdst + lane * N) = v;
   }
-  if (is_q) {
-    const float f = head_factor ? head_factor[head] : 1.f;
-    Run<T, N> o;
-#pragma unroll
-    for (int i = 0; i < N; ++i) o.v[i] = from_float<T>(x[i] * factor * f);
-    *reinterpret_cast<Run<T, N>*>(q_out + ((size_t)t * hq + head) * DIM + lane * N) = o;
-    return;
-  }
-  if (page < 0 || page >= num_pages) return;  // tables are checked on the host; never write outside the pool
-  const int g = head - hq;
-  const size_t slot = (size_t)(p % page_size);
-  TKV* dst = split_planes ? kv + ((((size_t)page * 2) * hkv + g) * page_size + slot) * DIM
-                          : kv + (((size_t)page * hkv + g) * page_size + slot) * (2 * DIM);
-  TKV* vdst = split_planes ? dst + (size_t)hkv * page_size * DIM : dst + DIM;
-  Run<TKV, N> k;
-#pragma unroll
-  for (int i = 0; i < N; ++i) k.v[i] = from_float<TKV>(x[i] * factor);
-  *reinterpret_cast<Run<TKV, N>*>(dst + lane * N) = k;
-  Run<T, N> vin = raw;
-  if (!values_are_keys) vin = *reinterpret_cast<const Run<T, N>*>(row + (size_t)(hq + hkv) * DIM + (size_t)g * DIM + lane * N);
-  Run<TKV, N> v;
-#pragma unroll
-  for (int i = 0; i < N; ++i) v.v[i] = from_float<TKV>(to_float<T>(vin.v[i]));
-  *reinterpret_cast<Run<TKV, N>*>(vdst + lane * N) = v;
 }
 
 }  // namespace
 
-#define PSB_PREP_ROWS(DD)                                                                                              \
-  psb_launch(attention_prepare_rows_kernel<T_, TKV, DD>, dim3((unsigned)blocks), dim3(PREP_WARPS * 32), 0, stream,     \
+#define PSB_PREP_ROWS(DD, HH)                                                                                          \
+  psb_launch(attention_prepare_rows_kernel<T_, TKV, DD, HH>, dim3((unsigned)blocks), dim3(PREP_WARPS * 32), 0, stream,     \
              (const T_*)proj, ld, (const int32_t*)positions, (const int32_t*)token_item, (const int32_t*)table,        \
              table_width, (const float*)cos_t, (const float*)sin_t, (const float*)head_factor, (TKV*)kv, (T_*)q_out,   \
              hq, hkv, page_size, num_pages, max_positions, rotary_dim, eps, values_are_keys, split_planes, groups)
@@ -193,7 +212,9 @@ PSB_API int psb_attention_prepare(const void* proj, long long ld, int dtype, con
   // heads in registers: sizes that give every lane an even run, a rotation (if any) of neighbours, rows that allow wide loads
   const bool rows_fit = vdim == dim && (dim == 64 || dim == 128 || dim == 256) && (cos_t == nullptr || interleaved);
   if (rows_fit) {
-    const int groups = (hq + hkv + PREP_WARPS - 1) / PREP_WARPS;
+    // long steps: four heads a warp, their loads in flight together; short ones: a head a warp, as many warps as there are heads
+    const int hpw = (long long)T * (hq + hkv) >= 4096 ? 4 : 1;
+    const int groups = (hq + hkv + PREP_WARPS * hpw - 1) / (PREP_WARPS * hpw);
     const long long blocks = (long long)T * groups;
     bool done = false;
     PSB_DISPATCH_DTYPE(dtype, T_, {
@@ -201,7 +222,11 @@ PSB_API int psb_attention_prepare(const void* proj, long long ld, int dtype, con
         const size_t in_run = sizeof(T_) * (size_t)(dim / 32), out_run = sizeof(TKV) * (size_t)(dim / 32);
         if (blocks <= 0x7fffffffLL && (uintptr_t)proj % in_run == 0 && ((size_t)ld * sizeof(T_)) % in_run == 0 &&
             (uintptr_t)q_out % in_run == 0 && (uintptr_t)kv % out_run == 0) {
-          if (dim == 64) PSB_PREP_ROWS(64); else if (dim == 128) PSB_PREP_ROWS(128); else PSB_PREP_ROWS(256);
+          if (hpw == 4) {
+            if (dim == 64) PSB_PREP_ROWS(64, 4); else if (dim == 128) PSB_PREP_ROWS(128, 4); else PSB_PREP_ROWS(256, 4);
+          } else {
+            if (dim == 64) PSB_PREP_ROWS(64, 1); else if (dim == 128) PSB_PREP_ROWS(128, 1); else PSB_PREP_ROWS(256, 1);
+          }
           done = true;
         }
       });

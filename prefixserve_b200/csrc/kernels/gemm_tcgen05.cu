@@ -68,7 +68,18 @@ using namespace tc;
 // mode: 0 plain (C[M, N], tile columns [n0, n0+BN/2) and [n0+BN/2, n0+BN)); 1 gated (C[M, I], W = [gate; up], tile
 // columns [n0, n0+128) of the gate and the same of the up rows); 2 the projection of an attention layer (columns as in
 // 0; the epilogue rotates queries and keys and stores queries, keys and values where RopeArgs says, C is not used).
-enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_ROPE = 2, MODE_GATED_GELU = 3, MODE_RELU2 = 4 };  // gated: SiLU, or the tanh form of GELU
+enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_ROPE = 2, MODE_GATED_GELU = 3, MODE_RELU2 = 4, MODE_GATED_CLIPPED = 5 };
+// gated: SiLU, the tanh form of GELU, or (clipped) g * sigmoid(alpha g) * (u + offset) with g = min(gate, limit) and
+// u = clamp(up, -limit, limit), the three numbers in GluArgs.
+struct GluArgs {
+  float limit, alpha, offset;
+};
+__device__ __forceinline__ bool mode_is_gated(int mode) { return mode == MODE_GATED || mode == MODE_GATED_GELU || mode == MODE_GATED_CLIPPED; }
+__device__ __forceinline__ float clipped_gate(float g, float u, const GluArgs& a) {
+  g = fminf(g, a.limit);
+  u = fminf(fmaxf(u, -a.limit), a.limit);
+  return g / (1.f + expf(-a.alpha * g)) * (u + a.offset);
+}
 // MODE_RELU2: columns as in 0, the epilogue stores max(sum, 0)^2.
 //
 // Grouped products (``tile_expert`` given): W is a stack of matrices [experts * N_out, K] and every 128-row tile of A
@@ -157,11 +168,11 @@ template <int BN, int HB>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     __nv_bfloat16* __restrict__ C, int M, int N_out, int K, int ldc, int up_offset, int mode,
-                    const RopeArgs rope, const int32_t* __restrict__ tile_expert) {
+                    const RopeArgs rope, const int32_t* __restrict__ tile_expert, const GluArgs glu) {
   using T = Tile<BN>;
   constexpr int BN_HALF = T::HALF, STAGES = T::STAGES, STAGE_BYTES = T::STAGE_BYTES;
   constexpr uint32_t INSTR_DESC = instr_desc(BM, BN, false);  // M=128, N=BN, both operands K-major
-  const bool gated = mode == MODE_GATED || mode == MODE_GATED_GELU;
+  const bool gated = mode_is_gated(mode);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Barriers* bars = reinterpret_cast<Barriers*>(tiles + STAGES * STAGE_BYTES);
@@ -312,6 +323,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const float u0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 2 * q])));
                 const float u1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[j + 2 * q + 1])));
                 packed[q] = mode == MODE_GATED ? pack2(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1)
+                            : mode == MODE_GATED_CLIPPED ? pack2(clipped_gate(g0, u0, glu), clipped_gate(g1, u1, glu))
                                                : pack2(gate_act(g0, PSB_ACT_GELU_TANH) * u0, gate_act(g1, PSB_ACT_GELU_TANH) * u1);
               }
               if (col + 8 <= N_out && (ldc & 7) == 0) {
@@ -409,8 +421,9 @@ int choose_width(int M, int N_out, bool gated, bool rope, int D, int sms) {
 }
 
 int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, int K, int up_offset, int mode, int sms,
-           cudaStream_t stream, const RopeArgs& rope = RopeArgs{}, const int32_t* tile_expert = nullptr) {
-  const bool gated = mode == MODE_GATED || mode == MODE_GATED_GELU;
+           cudaStream_t stream, const RopeArgs& rope = RopeArgs{}, const int32_t* tile_expert = nullptr,
+           const GluArgs& glu = GluArgs{}) {
+  const bool gated = mode == MODE_GATED || mode == MODE_GATED_GELU || mode == MODE_GATED_CLIPPED;
   if (M < 1 || N_out < 1 || K < 8 || K % 8) PSB_REFUSE("gemm_tcgen05: needs K a multiple of 8 (M=%d N=%d K=%d)", M, N_out, K);
   if (((uintptr_t)a | (uintptr_t)w | (uintptr_t)c) & 15) PSB_REFUSE("gemm_tcgen05: operands must be 16-byte aligned");
   const int m_blocks = (M + BM - 1) / BM;
@@ -431,7 +444,7 @@ int launch(const void* a, const void* w, void* c, int M, int w_rows, int N_out, 
       configured.set();                                                                                              \
     }                                                                                                                \
     psb_launch(gemm_tcgen05_kernel<BN, HB>, dim3(grid), dim3(THREADS), (size_t)Tile<BN>::SMEM_BYTES, stream, map_a,   \
-               map_w, (__nv_bfloat16*)c, M, N_out, K, N_out, up_offset, mode, rope, tile_expert);                    \
+               map_w, (__nv_bfloat16*)c, M, N_out, K, N_out, up_offset, mode, rope, tile_expert, glu);               \
   } while (0)
   // the usual head sizes keep a row's angles in registers; every other multiple of 16 fetches them block by block
   if (mode == MODE_ROPE && rope.D == 128) { if (bn == 128) PSB_TCGEN05(128, 8); else PSB_TCGEN05(256, 8); }
@@ -457,6 +470,14 @@ PSB_API int psb_gemm_tcgen05_gated(const void* a, const void* w, void* act, int 
                                    cudaStream_t stream) {
   if (!psb_activation_known(activation)) PSB_REFUSE("gemm_tcgen05_gated: activation code %d is not built", activation);
   return launch(a, w, act, M, 2 * I, I, K, I, activation == PSB_ACT_SILU ? MODE_GATED : MODE_GATED_GELU, sms, stream);
+}
+
+// The same with both branches clipped before they meet: act = g * sigmoid(alpha g) * (u + offset), g = min(A Wg^T, limit),
+// u = clamp(A Wu^T, -limit, limit), both rounded to bfloat16 first, as the product without the activation would leave them.
+PSB_API int psb_gemm_tcgen05_gated_clipped(const void* a, const void* w, void* act, int M, int I, int K, int sms, float limit,
+                                           float alpha, float offset, cudaStream_t stream) {
+  if (!(limit > 0.f)) PSB_REFUSE("gemm_tcgen05_gated_clipped: the limit must be positive");
+  return launch(a, w, act, M, 2 * I, I, K, I, MODE_GATED_CLIPPED, sms, stream, RopeArgs{}, nullptr, GluArgs{limit, alpha, offset});
 }
 
 // Grouped: C[M, N] = act(A[M, K] W[e]^T) where W is [experts, N, K] and the rows of A lie expert by expert, every

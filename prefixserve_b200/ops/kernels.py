@@ -1051,7 +1051,9 @@ def attention_prepare(proj: torch.Tensor, kv: torch.Tensor, table: torch.Tensor,
     return q
 
 
-MIN_GRU_CHUNK = 64  # portions of more than twice this many tokens run as chunks side by side
+# Portions of more than four times this many tokens run as chunks side by side.  32: a 2,048-token portion at width 2,048
+# gives 2,112 blocks of two warps, 28 warps an SM; with chunks of 64 an SM held 14 and the two passes took 24 + 35 us.
+MIN_GRU_CHUNK = 32
 
 
 def min_gru(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, state: torch.Tensor, ctx, *, width: int) -> torch.Tensor:
@@ -1064,7 +1066,7 @@ def min_gru(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, stat
     stride = _slot_rows(state, width, "minGRU state")
     _f32_vector(bias_z, width, "update-gate bias"), _f32_vector(bias_x, width, "candidate bias")
     out = torch.empty((t, width), dtype=proj.dtype, device=proj.device)
-    two_pass = ctx.max_new_tokens > 2 * MIN_GRU_CHUNK
+    two_pass = ctx.max_new_tokens > 4 * MIN_GRU_CHUNK
     chunk = MIN_GRU_CHUNK if two_pass else max(t, 1)
     carry = start = None
     if two_pass:
@@ -1075,6 +1077,23 @@ def min_gru(proj: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, stat
                             _i32(ctx.slots, "slots").data_ptr(), _ptr(carry), _ptr(start), out.data_ptr(), ctx.num_items, t, width,
                             state.shape[0], chunk, 1 if two_pass else 0, _stream()), "min_gru")
     return out
+
+
+CLIPPED_FUSED_MIN_ROWS = 65  # from here on no product folds the norm in front of it into itself, so nothing is lost by asking for the rows
+
+
+def clipped_gated_linear(x, w_gate_up: torch.Tensor, limit: float, alpha: float = 1.702, offset: float = 1.0) -> torch.Tensor:
+    """g * sigmoid(alpha g) * (u + offset) with g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit) for W = [gate rows;
+    up rows]: many bfloat16 rows in the product's epilogue, else product (which may fold the norm in front into itself)
+    and then the activation.  Both ways round the two products to the compute type before they are clipped."""
+    if x.shape[0] >= CLIPPED_FUSED_MIN_ROWS and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16:
+        from .tensorcore import clipped_gated_linear_bf16
+        rows = x.tensor() if isinstance(x, NormedRows) else x
+        act = clipped_gated_linear_bf16(rows, w_gate_up, limit, alpha, offset)
+        if act is not None:
+            return act
+        x = rows
+    return clipped_glu(linear(x, w_gate_up), limit, alpha, offset)
 
 
 def clipped_glu(gate_up: torch.Tensor, limit: float, alpha: float = 1.702, offset: float = 1.0) -> torch.Tensor:

@@ -84,6 +84,8 @@ _SIGNATURES: dict[str, list] = {
     "psb_gemm_tcgen05": [P, P, P, I, I, I, I, P],
     # (a, w, act, M, I, K, sms, activation, stream)
     "psb_gemm_tcgen05_gated": [P, P, P, I, I, I, I, I, P],
+    # (a, w, act, M, I, K, sms, limit, alpha, offset, stream)
+    "psb_gemm_tcgen05_gated_clipped": [P, P, P, I, I, I, I, F, F, F, P],
     "psb_gemm_tcgen05_tile_width": [I],
     # (M, N_out, kind, D, sms) -> output tiles at the width the kernel would choose
     "psb_gemm_tcgen05_tiles": [I, I, I, I, I],

@@ -277,6 +277,19 @@ def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int
     return act
 
 
+def clipped_gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, limit: float, alpha: float, offset: float) -> torch.Tensor | None:
+    """g * sigmoid(alpha g) * (u + offset) with g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit), in the epilogue
+    of the tcgen05 product; None when that kernel does not take the shape (few rows, sizes)."""
+    m, k = x.shape
+    if w_gate_up.shape[0] % 2 or m <= STREAM_M or not _tcgen05_ok(x, w_gate_up, 1):
+        return None
+    inter = w_gate_up.shape[0] // 2
+    act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
+    check(lib().psb_gemm_tcgen05_gated_clipped(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, _sms(x.device),
+                                               float(limit), float(alpha), float(offset), stream_handle()), "gemm_tcgen05_gated_clipped")
+    return act
+
+
 def tcgen05_qkv_rope_bf16(x: torch.Tensor, w_qkv, positions, token_item, cos, sin, table, kv, hq, hkv, d, page_size) -> torch.Tensor | None:
     """The projection of an attention layer for many tokens on the tcgen05 kernel, rotation and append to the pages in
     its epilogue (for a few dozen tokens: on the few-row kernel, which does the same); None when neither takes the shape."""

@@ -50,7 +50,7 @@ class GatedMLP(FeedForward):
 
     def forward(self, x, ctx: StepContext):
         if self.clipped:
-            act = ops.clipped_glu(ops.linear(x, self.w_gate_up), self.limit, self.gate_alpha, self.up_offset)
+            act = ops.clipped_gated_linear(x, self.w_gate_up, self.limit, self.gate_alpha, self.up_offset)
             return ops.last_product(act, self.w_down, ctx)
         return ops.last_product(ops.gated_linear(x, self.w_gate_up, self.activation), self.w_down, ctx)
 

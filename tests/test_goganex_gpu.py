@@ -364,10 +364,10 @@ def test_prepared_attention_alone(shape, steps, planes, dtype):
     kv, table = paged_entry(hkv, dim + vdim if planes == 1 else dim, page, total, dtype, planes=planes)
     outs = {}
     for step, (lengths, starts) in enumerate((([h for h in had if h], [0 for h in had if h]), (new, had))):
-        items = [i for i, h in enumerate(had) if h] if step == 0 else [0, 1, 2]
+        items = [i for i, h in enumerate(had) if h] if step == 0 else list(range(len(had)))
         rows = torch.cat([seqs[i][s: s + n] for i, n, s in zip(items, lengths, starts)]).cuda()
         ctx = step_context(lengths, starts, items)
-        tab = table[items].contiguous()
+        tab = table.cpu()[items].contiguous().cuda()   # rows picked on the host: a wrong index raises here, not on the device
         q = ops.attention_prepare(rows, kv, tab, ctx, num_heads=hq, num_kv_heads=hkv, dim=dim, vdim=vdim, page_size=page,
                                   cos=cos, sin=sin, rotary_dim=rotated, interleaved=interleaved, unit_norm_eps=eps if unit else None,
                                   head_factor=None if temp is None else temp.cuda(), values_are_keys=keys,
@@ -449,6 +449,22 @@ def test_clipped_gate_alone(dtype):
         got = ops.clipped_glu(z.cuda(), limit).cpu().double()
         want = plain.feed_forward({"limit": limit}, {"f.gate": torch.cat([eye, 0 * eye], 1), "f.up": torch.cat([0 * eye, eye], 1), "f.down": eye}, "f.", x)
         assert torch.allclose(got, want, atol=1e-5 if dtype == torch.float32 else 3e-2, rtol=0 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("rows", [40, 1024])
+def test_clipped_gated_product_alone(rows):
+    """Both products and the clipped gate as one op (many bfloat16 rows: in the product's epilogue; few: product, then
+    gate) against the plain feed-forward with an identity behind it."""
+    from prefixserve_b200 import ops
+    g = torch.Generator().manual_seed(rows)
+    width, ff = 256, 2048
+    x = torch.randn(rows, width, generator=g).to(torch.bfloat16)
+    w = (1.5 * torch.randn(2 * ff, width, generator=g) / width ** 0.5).to(torch.bfloat16)
+    eye = torch.eye(ff, dtype=torch.float64)
+    for limit in (0.7, 7.0):
+        got = ops.clipped_gated_linear(x.cuda(), w.cuda(), limit).cpu().double()
+        want = plain.feed_forward({"limit": limit}, {"f.gate": w[:ff].double(), "f.up": w[ff:].double(), "f.down": eye}, "f.", x.double())
+        assert got.shape == want.shape and torch.allclose(got, want, atol=4e-2, rtol=2e-2)
 
 
 # ---- generation through the scheduler --------------------------------------------------------------------------
