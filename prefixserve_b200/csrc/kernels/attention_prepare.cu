@@ -14,8 +14,8 @@
 //
 // Two kernels.  The general one: one block per token, a warp per head in turn; the head lies in the warp's
 // shared-memory row between the steps.  The other, for heads of 64, 128 or 256 elements whose rotation (if any) pairs
-// neighbours: a warp per (token, head) or per (token, four heads), the head in registers (every lane a run of dim/32 elements, which holds whole
-// pairs), one wide load and one wide store per lane and row.
+// neighbours: the head in registers, 32 or 16 lanes a head (every lane a run of elements, which holds whole pairs), one
+// wide load and one wide store per lane and row, a warp taking one or several heads.
 // Rotation, statistics and factors are float32; storage is float32 or bfloat16.
 #include "common.cuh"
 
@@ -93,10 +93,13 @@ struct alignas(sizeof(T) * N) Run {
   T v[N];
 };
 
-// grid: T * groups blocks, groups = ceil((hq + hkv) / (PREP_WARPS * HPW)); warp w of block b: token b / groups, heads
-// ((b % groups) * PREP_WARPS + w) * HPW .. + HPW - 1.  HPW > 1 (long steps): the rows of a warp's heads are asked for
-// together, before any of them is used, so that a lane has several loads in flight.
-template <typename T, typename TKV, int DIM, int HPW>
+// grid: T * groups blocks.  LPH lanes hold a head (32, or 16 for heads of 64 when both head counts are even: then a lane has
+// four elements instead of two and a warp takes two heads at a time, which halves the instructions a byte costs); a warp
+// takes HPW rounds of 32 / LPH heads: heads (warp index in the token * HPW + round) * (32 / LPH) + lane / LPH.  HPW > 1 (long
+// steps): the rows of all of a warp's rounds are asked for together, before any of them is used, so that a lane has
+// several loads in flight.  groups = ceil((hq + hkv) / (PREP_WARPS * HPW * 32 / LPH)).  A round lies within the heads or
+// beyond them as a whole (the head counts are multiples of 32 / LPH), so the shuffles of a round see all of its lanes.
+template <typename T, typename TKV, int DIM, int HPW, int LPH>
 __global__ void __launch_bounds__(PREP_WARPS * 32)
 attention_prepare_rows_kernel(const T* __restrict__ proj, long long ld, const int32_t* __restrict__ positions,
                               const int32_t* __restrict__ token_item, const int32_t* __restrict__ table, int table_width,
@@ -104,11 +107,13 @@ attention_prepare_rows_kernel(const T* __restrict__ proj, long long ld, const in
                               const float* __restrict__ head_factor, TKV* __restrict__ kv, T* __restrict__ q_out, int hq, int hkv,
                               int page_size, int num_pages, int max_positions, int rotary_dim, float eps, int values_are_keys,
                               int split_planes, int groups) {
-  constexpr int N = DIM / 32;
+  constexpr int N = DIM / LPH;    // elements a lane holds
+  constexpr int HPR = 32 / LPH;   // heads a round
   pdl_trigger();
   const int t = blockIdx.x / groups;
-  const int head0 = ((blockIdx.x - t * groups) * PREP_WARPS + (threadIdx.x >> 5)) * HPW;
   const int lane = threadIdx.x & 31;
+  const int sub = lane / LPH, sl = lane % LPH;
+  const int head0 = ((blockIdx.x - t * groups) * PREP_WARPS + (threadIdx.x >> 5)) * HPW * HPR;
   // positions and tables are inputs of the step: they may be read before the preceding kernel has finished
   const int p = positions[t];
   const int page = table[(size_t)token_item[t] * table_width + p / page_size];
@@ -119,32 +124,32 @@ attention_prepare_rows_kernel(const T* __restrict__ proj, long long ld, const in
   Run<T, N> raw[HPW], vin[HPW];
 #pragma unroll
   for (int i = 0; i < HPW; ++i) {
-    const int head = head0 + i;
-    if (head < heads) raw[i] = *reinterpret_cast<const Run<T, N>*>(row + (size_t)head * DIM + lane * N);
+    const int head = head0 + i * HPR + sub;
+    if (head < heads) raw[i] = *reinterpret_cast<const Run<T, N>*>(row + (size_t)head * DIM + sl * N);
     if (head < heads && head >= hq && !values_are_keys)
-      vin[i] = *reinterpret_cast<const Run<T, N>*>(row + (size_t)heads * DIM + (size_t)(head - hq) * DIM + lane * N);
+      vin[i] = *reinterpret_cast<const Run<T, N>*>(row + (size_t)heads * DIM + (size_t)(head - hq) * DIM + sl * N);
   }
   const bool turn = cos_t != nullptr && p >= 0 && p < max_positions;
   float cs[N / 2], sn[N / 2];
   if (turn) {
 #pragma unroll
     for (int i = 0; i < N; i += 2) {
-      const int d = lane * N + i;  // even: the pair (d, d + 1) turns by angle d / 2
+      const int d = sl * N + i;  // even: the pair (d, d + 1) turns by angle d / 2
       cs[i / 2] = d < rotary_dim ? cos_t[(size_t)p * (rotary_dim / 2) + (d >> 1)] : 1.f;
       sn[i / 2] = d < rotary_dim ? sin_t[(size_t)p * (rotary_dim / 2) + (d >> 1)] : 0.f;
     }
   }
 #pragma unroll
   for (int hh = 0; hh < HPW; ++hh) {
-    const int head = head0 + hh;
-    if (head >= heads) break;
+    const int head = head0 + hh * HPR + sub;
+    if (head0 + hh * HPR >= heads) break;  // the whole round lies beyond the heads
     float x[N];
 #pragma unroll
     for (int i = 0; i < N; ++i) x[i] = to_float<T>(raw[hh].v[i]);
     if (turn) {
 #pragma unroll
       for (int i = 0; i < N; i += 2) {
-        if (lane * N + i < rotary_dim) {
+        if (sl * N + i < rotary_dim) {
           float o1, o2;
           rotate_pair(x[i], x[i + 1], cs[i / 2], sn[i / 2], o1, o2);
           x[i] = o1;
@@ -157,14 +162,17 @@ attention_prepare_rows_kernel(const T* __restrict__ proj, long long ld, const in
       float ss = 0.f;
 #pragma unroll
       for (int i = 0; i < N; ++i) ss = fmaf(x[i], x[i], ss);
-      factor = 1.f / sqrtf(warp_sum(ss) / (float)DIM + eps);
+#pragma unroll
+      for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);  // over the head's lanes
+      factor = 1.f / sqrtf(ss / (float)DIM + eps);
     }
+    if (head >= heads) continue;  // cannot happen while the head counts are multiples of a round; never store for a head that is not there
     if (head < hq) {
       const float f = head_factor ? head_factor[head] : 1.f;
       Run<T, N> o;
 #pragma unroll
       for (int i = 0; i < N; ++i) o.v[i] = from_float<T>(x[i] * factor * f);
-      *reinterpret_cast<Run<T, N>*>(q_out + ((size_t)t * hq + head) * DIM + lane * N) = o;
+      *reinterpret_cast<Run<T, N>*>(q_out + ((size_t)t * hq + head) * DIM + sl * N) = o;
       continue;
     }
     if (page < 0 || page >= num_pages) continue;  // tables are checked on the host; never write outside the pool
@@ -176,19 +184,19 @@ attention_prepare_rows_kernel(const T* __restrict__ proj, long long ld, const in
     Run<TKV, N> k;
 #pragma unroll
     for (int i = 0; i < N; ++i) k.v[i] = from_float<TKV>(x[i] * factor);
-    *reinterpret_cast<Run<TKV, N>*>(dst + lane * N) = k;
+    *reinterpret_cast<Run<TKV, N>*>(dst + sl * N) = k;
     const Run<T, N> vsrc = values_are_keys ? raw[hh] : vin[hh];
     Run<TKV, N> v;
 #pragma unroll
     for (int i = 0; i < N; ++i) v.v[i] = from_float<TKV>(to_float<T>(vsrc.v[i]));
-    *reinterpret_cast<Run<TKV, N>*>(vdst + lane * N) = v;
+    *reinterpret_cast<Run<TKV, N>*>(vdst + sl * N) = v;
   }
 }
 
 }  // namespace
 
-#define PSB_PREP_ROWS(DD, HH)                                                                                          \
-  psb_launch(attention_prepare_rows_kernel<T_, TKV, DD, HH>, dim3((unsigned)blocks), dim3(PREP_WARPS * 32), 0, stream,     \
+#define PSB_PREP_ROWS(DD, HH, LL)                                                                                      \
+  psb_launch(attention_prepare_rows_kernel<T_, TKV, DD, HH, LL>, dim3((unsigned)blocks), dim3(PREP_WARPS * 32), 0, stream,     \
              (const T_*)proj, ld, (const int32_t*)positions, (const int32_t*)token_item, (const int32_t*)table,        \
              table_width, (const float*)cos_t, (const float*)sin_t, (const float*)head_factor, (TKV*)kv, (T_*)q_out,   \
              hq, hkv, page_size, num_pages, max_positions, rotary_dim, eps, values_are_keys, split_planes, groups)
@@ -214,18 +222,23 @@ PSB_API int psb_attention_prepare(const void* proj, long long ld, int dtype, con
   if (rows_fit) {
     // long steps: four heads a warp, their loads in flight together; short ones: a head a warp, as many warps as there are heads
     const int hpw = (long long)T * (hq + hkv) >= 4096 ? 4 : 1;
-    const int groups = (hq + hkv + PREP_WARPS * hpw - 1) / (PREP_WARPS * hpw);
+    // heads of 64 in pairs (16 lanes a head, four elements a lane) when neither the query nor the key heads leave one over
+    const int lph = dim == 64 && hq % 2 == 0 && hkv % 2 == 0 ? 16 : 32;
+    const int per_block = PREP_WARPS * hpw * (32 / lph);
+    const int groups = (hq + hkv + per_block - 1) / per_block;
     const long long blocks = (long long)T * groups;
     bool done = false;
     PSB_DISPATCH_DTYPE(dtype, T_, {
       PSB_DISPATCH_DTYPE(kv_dtype, TKV, {
-        const size_t in_run = sizeof(T_) * (size_t)(dim / 32), out_run = sizeof(TKV) * (size_t)(dim / 32);
+        const size_t in_run = sizeof(T_) * (size_t)(dim / lph), out_run = sizeof(TKV) * (size_t)(dim / lph);
         if (blocks <= 0x7fffffffLL && (uintptr_t)proj % in_run == 0 && ((size_t)ld * sizeof(T_)) % in_run == 0 &&
             (uintptr_t)q_out % in_run == 0 && (uintptr_t)kv % out_run == 0) {
           if (hpw == 4) {
-            if (dim == 64) PSB_PREP_ROWS(64, 4); else if (dim == 128) PSB_PREP_ROWS(128, 4); else PSB_PREP_ROWS(256, 4);
+            if (dim == 64 && lph == 16) PSB_PREP_ROWS(64, 4, 16); else if (dim == 64) PSB_PREP_ROWS(64, 4, 32);
+            else if (dim == 128) PSB_PREP_ROWS(128, 4, 32); else PSB_PREP_ROWS(256, 4, 32);
           } else {
-            if (dim == 64) PSB_PREP_ROWS(64, 1); else if (dim == 128) PSB_PREP_ROWS(128, 1); else PSB_PREP_ROWS(256, 1);
+            if (dim == 64 && lph == 16) PSB_PREP_ROWS(64, 1, 16); else if (dim == 64) PSB_PREP_ROWS(64, 1, 32);
+            else if (dim == 128) PSB_PREP_ROWS(128, 1, 32); else PSB_PREP_ROWS(256, 1, 32);
           }
           done = true;
         }

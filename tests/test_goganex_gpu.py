@@ -209,12 +209,13 @@ def test_a_long_memory_survives_portions_and_decoding(tmp_path):
         assert worst_error(replay(folder, "float32", steps), truth) < LIMIT["float32"]
 
 
-def test_long_decoding(made):
+@pytest.mark.parametrize("which", ["whole_loop", "planes"])
+def test_long_decoding(made, which):
     """Hundreds of single tokens behind a short prompt, several requests side by side in captured steps."""
-    cfg = gm.CONFIGS["whole_loop"]
+    cfg = gm.CONFIGS[which]
     for dtype in ("float32", "bfloat16"):
-        folder, _ = made["whole_loop", dtype]
-        _, exact = stored(gm.tensors(cfg, seed=sorted(gm.CONFIGS).index("whole_loop")), dtype)
+        folder, _ = made[which, dtype]
+        _, exact = stored(gm.tensors(cfg, seed=sorted(gm.CONFIGS).index(which)), dtype)
         seqs = sequences(cfg["vocab"], lengths=[400, 260, 333], seed=60)
         truth = {rid: plain.forward(cfg, exact, toks) for rid, toks in seqs.items()}
         steps = helpers.trace_many_live(seqs, tail=250, portion_beside=False)
