@@ -130,6 +130,69 @@ token_shift_kernel(const T* __restrict__ x, const float* __restrict__ mix, float
   }
 }
 
+// Steps of single tokens: the residual sum, the RMS norm in front of the shifted sublayer and the shift in one kernel,
+//
+//   h_t += delta_t        n_t = round(gain * h_t / rms(h_t))        y_t = n_t + (held - n_t) * mix        held <- n_t
+//
+// with ``held`` the request's carried row (zero for a sequence's first token) and ``round`` the rounding to the rows'
+// type that the norm's own kernel would do, so that a token gets the same y whichever way it went.  A block per token;
+// every token of the step is its request's only one, so no block needs another's row.  W % 8 == 0.
+template <typename TD, typename TX>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_shift_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ gain, float eps,
+                         const float* __restrict__ mix, float* __restrict__ state, long long stride,
+                         const int32_t* __restrict__ positions, const int32_t* __restrict__ token_item,
+                         const int32_t* __restrict__ slots, TX* __restrict__ y, int W, int num_slots) {
+  __shared__ float sums[8];
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int slot = slots[token_item[t]];
+  const bool starts = positions[t] == 0;
+  pdl_wait();
+  float* hr = h + (size_t)t * W;
+  float ss = 0.f;
+  for (int c = threadIdx.x * 8; c < W; c += blockDim.x * 8) {
+    float v[8];
+    run8_load<float>(hr + c, v);
+    if (delta) {
+      float d[8];
+      run8_load<TD>(delta + (size_t)t * W + c, d);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] += d[k];
+      run8_store<float>(hr + c, v);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss = fmaf(v[k], v[k], ss);
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) sums[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  ss = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) ss += sums[w];
+  const float inv = rsqrtf(ss / (float)W + eps);
+  if (slot < 0 || slot >= num_slots) return;  // slots are checked on the host; never touch memory outside the states
+  float* held = state + (size_t)slot * stride;
+  for (int c = threadIdx.x * 8; c < W; c += blockDim.x * 8) {  // a thread meets the channels it wrote above
+    float v[8], g[8], m[8], b[8];
+    run8_load<float>(hr + c, v);
+    run8_load<float>(gain + c, g);
+    run8_load<float>(mix + c, m);
+    if (starts) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) b[k] = 0.f;
+    } else {
+      run8_load<float>(held + c, b);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      v[k] = to_float<TX>(from_float<TX>(g[k] * (v[k] * inv)));
+      b[k] = fmaf(b[k] - v[k], m[k], v[k]);
+    }
+    run8_store<TX>(y + (size_t)t * W + c, b);
+    run8_store<float>(held + c, v);
+  }
+}
+
 // out = (gain_a * a / rms(a) + gain_b * b / rms(b)) * weight: two branches that read the same input, each normed over
 // the row before they are added.  One block per row, statistics float32, float32 result.
 template <typename T, bool VEC>
@@ -203,6 +266,27 @@ PSB_API int psb_token_shift(const void* x, int dtype, const void* mix, void* sta
                (const int32_t*)slots, (T_*)y, W, num_slots);
   });
   PSB_LAUNCH_CHECK("token_shift");
+  return 0;
+}
+
+// (h, delta, delta_dtype, gain, eps, mix, state, stride, positions, token_item, slots, y, y_dtype, T, W, num_slots, stream)
+// Every token of the step must be its request's only one (the caller knows: the step's longest portion is one token).
+PSB_API int psb_add_rmsnorm_shift(void* h, const void* delta, int delta_dtype, const void* gain, float eps, const void* mix,
+                                  void* state, long long stride, const void* positions, const void* token_item,
+                                  const void* slots, void* y, int y_dtype, int T, int W, int num_slots, cudaStream_t stream) {
+  if (T < 0 || W < 8 || W % 8 || num_slots < 1 || stride < W || stride % 4) PSB_REFUSE("add_rmsnorm_shift: bad sizes T=%d W=%d stride=%lld", T, W, stride);
+  if (!(eps > 0.f)) PSB_REFUSE("add_rmsnorm_shift: eps must be positive");
+  if (((uintptr_t)h | (uintptr_t)delta | (uintptr_t)gain | (uintptr_t)mix | (uintptr_t)state | (uintptr_t)y) & 15)
+    PSB_REFUSE("add_rmsnorm_shift: operands must be 16-byte aligned");
+  if (T == 0) return 0;
+  PSB_DISPATCH_DTYPE(delta_dtype, TD, {
+    PSB_DISPATCH_DTYPE(y_dtype, TX, {
+      psb_launch(add_rmsnorm_shift_kernel<TD, TX>, dim3(T), dim3(W >= 2048 ? 256 : 128), 0, stream, (float*)h, (const TD*)delta,
+                 (const float*)gain, eps, (const float*)mix, (float*)state, stride, (const int32_t*)positions,
+                 (const int32_t*)token_item, (const int32_t*)slots, (TX*)y, W, num_slots);
+    });
+  });
+  PSB_LAUNCH_CHECK("add_rmsnorm_shift");
   return 0;
 }
 

@@ -976,14 +976,33 @@ def _slot_rows(state: torch.Tensor, width: int, what: str) -> int:
     return int(state.stride(0))
 
 
-def token_shift(x: torch.Tensor, mix: torch.Tensor, state: torch.Tensor, ctx) -> torch.Tensor:
+FUSE_NORM_SHIFT = True  # steps of single tokens: the residual sum, the norm in front and the shift in one kernel
+
+
+def token_shift(x, mix: torch.Tensor, state: torch.Tensor, ctx) -> torch.Tensor:
     """y_t = x_t + (x_(t-1) - x_t) * mix per channel, with x_(t-1) the row before (zero in front of a sequence's first
     token); the row before a portion's first token comes from ``state`` [num_slots, W] (float32; rows may be strided),
-    which receives the portion's last row."""
-    _dev(x, "shifted rows")
+    which receives the portion's last row.  ``x`` may be an ``ops.NormedRows`` that nobody has computed yet: in a step
+    of single tokens the residual sum and the norm then run in the same kernel as the shift."""
     t, w = x.shape
     stride = _slot_rows(state, w, "token-shift state")
     _f32_vector(mix, w, "token-shift weights")
+    if isinstance(x, NormedRows):
+        if (FUSE_NORM_SHIFT and ctx.max_new_tokens == 1 and x._x is None and not x._settled and x.rows is None and w % 8 == 0
+                and stride % 4 == 0 and state.data_ptr() % 16 == 0):
+            pending = x.pending.tensor() if isinstance(x.pending, PendingProduct) else x.pending
+            if pending is None or (pending.is_contiguous() and pending.shape == x.h.shape and pending.data_ptr() % 16 == 0):
+                _dev(x.h, "residual stream")
+                y = torch.empty((t, w), dtype=x.dtype, device=x.h.device)
+                check(lib().psb_add_rmsnorm_shift(x.h.data_ptr(), _ptr(pending), _code(pending, "sublayer output") if pending is not None else F32,
+                                                  x.gain.data_ptr(), x.eps, mix.data_ptr(), state.data_ptr(), stride,
+                                                  _i32(ctx.positions, "positions").data_ptr(), _i32(ctx.token_item, "token-to-item map").data_ptr(),
+                                                  _i32(ctx.slots, "slots").data_ptr(), y.data_ptr(), _code(y, "shifted rows"), t, w,
+                                                  state.shape[0], _stream()), "add_rmsnorm_shift")
+                x.fused(None)
+                return y
+        x = x.tensor()
+    _dev(x, "shifted rows")
     y = torch.empty_like(x)
     check(lib().psb_token_shift(x.data_ptr(), _code(x, "shifted rows"), mix.data_ptr(), state.data_ptr(), stride,
                                 _i32(ctx.positions, "positions").data_ptr(), _i32(ctx.token_item, "token-to-item map").data_ptr(),

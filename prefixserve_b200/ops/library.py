@@ -193,6 +193,8 @@ _SIGNATURES: dict[str, list] = {
     "psb_moe_combine": [P, I, P, P, P, I, P, I, P, I, I, I, I, P],
     # (x, dtype, mix, state, stride, positions, token_item, item_start, slots, y, T, W, num_slots, stream)
     "psb_token_shift": [P, I, P, P, L, P, P, P, P, P, I, I, I, P],
+    # (h, delta, delta_dtype, gain, eps, mix, state, stride, positions, token_item, slots, y, y_dtype, T, W, num_slots, stream)
+    "psb_add_rmsnorm_shift": [P, P, I, P, F, P, P, L, P, P, P, P, I, I, I, I, P],
     # (a, b, dtype, gain_a, gain_b, out_f32, T, W, eps, weight, stream)
     "psb_normed_pair_sum": [P, P, I, P, P, P, I, I, F, F, P],
     # (proj, ld, dtype, positions, token_item, table, table_width, cos, sin, head_factor, kv, kv_dtype, q_out, T, hq, hkv, dim, vdim,

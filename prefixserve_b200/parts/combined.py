@@ -49,6 +49,8 @@ def _inner_view(cache: CacheView, need: CacheNeed, at: int, count: int, alone: b
 
 
 class TokenShifted(Mixer):
+    takes_deferred_input = True  # x goes to the shift only, which may do the sum and the norm in front of it itself
+
     def __init__(self, params):
         super().__init__(params)
         self.size = int(params["size"])

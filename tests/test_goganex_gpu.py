@@ -279,6 +279,46 @@ def test_token_shift_alone(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [24, 2056])
+@pytest.mark.parametrize("with_delta", [False, True])
+def test_sum_norm_and_shift_in_one_kernel(dtype, width, with_delta):
+    """A step of single tokens hands the shift a norm that has not run: stream += delta, norm and shift against the
+    plain functions, the stream and the carried row left as the separate kernels leave them."""
+    from prefixserve_b200 import ops
+    g = torch.Generator().manual_seed(width)
+    starts, slots = [0, 9, 4, 0], [2, 0, 3, 1]
+    lengths = [1] * len(starts)
+    h = torch.randn(len(starts), width, generator=g)
+    delta = torch.randn(len(starts), width, generator=g).to(dtype) if with_delta else None
+    gain, mix, eps = 1 + 0.1 * torch.randn(width, generator=g), torch.rand(width, generator=g), 1e-5
+    wide = torch.randn(5, width + 16, generator=g)
+    ctx = step_context(lengths, starts, slots)
+    results = []
+    for fused in (True, False):
+        ops.kernels.FUSE_NORM_SHIFT = fused
+        try:
+            stream, state = h.clone().cuda(), wide.clone().cuda()
+            x = ops.NormedRows(stream, None if delta is None else delta.cuda(), gain.cuda(), eps, dtype)
+            y = ops.token_shift(x, mix.cuda(), state[:, :width], ctx)
+            assert x.residual() is stream
+        finally:
+            ops.kernels.FUSE_NORM_SHIFT = True
+        results.append((y.cpu().double(), stream.cpu(), state.cpu()))
+    summed = h.double() + (0 if delta is None else delta.double())
+    normed = plain.norm(summed, gain.double(), eps)
+    for y, stream, state in results:
+        assert torch.allclose(stream.double(), summed, atol=1e-6)
+        for i, (s, slot) in enumerate(zip(starts, slots)):
+            first = torch.zeros(1, width, dtype=torch.float64) if s == 0 else wide[slot, :width].double()[None]
+            want = plain.token_shift(torch.cat([first, normed[i: i + 1]]), mix.double())[1:]
+            assert torch.allclose(y[i: i + 1], want, atol=1e-5 if dtype == torch.float32 else 3e-2)
+            assert torch.allclose(state[slot, :width].double(), normed[i], atol=1e-5 if dtype == torch.float32 else 2e-2)
+        assert torch.equal(state[:, width:], wide[:, width:]) and torch.equal(state[4], wide[4])
+    # one kernel or two: the same rows up to the last bit of the norm's factor
+    assert torch.allclose(results[0][0], results[1][0], atol=1e-6 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("lengths", [[1, 1, 1], [5, 1, 40], [300, 2, 129, 64, 1]])   # the last: chunks that run side by side
 def test_min_gru_alone(dtype, lengths):
     from prefixserve_b200 import ops
