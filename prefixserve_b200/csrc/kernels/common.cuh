@@ -115,6 +115,23 @@ __device__ __forceinline__ float gate_act(float g, int act) {
   return g / (1.f + expf(-g));
 }
 
+// A gated feed-forward whose two branches are clipped before they meet: g = min(gate, limit), u = clamp(up, -limit, limit),
+// value = g * sigmoid(alpha * g) * (u + offset).  It has numbers of its own, so it is no PsbAct code that every entry
+// point takes: kernels that know it receive PSB_ACT_CLIPPED together with a GluClip.
+constexpr int PSB_ACT_CLIPPED = 2;
+struct GluClip {
+  float limit, alpha, offset;
+};
+__device__ __forceinline__ float clipped_gate_value(float g, float u, const GluClip& c) {
+  g = fminf(g, c.limit);
+  u = fminf(fmaxf(u, -c.limit), c.limit);
+  return g / (1.f + expf(-c.alpha * g)) * (u + c.offset);
+}
+// act(gate) * up for a PsbAct code, or the clipped form
+__device__ __forceinline__ float gated_value(float g, float u, int act, const GluClip& c) {
+  return act == PSB_ACT_CLIPPED ? clipped_gate_value(g, u, c) : gate_act(g, act) * u;
+}
+
 template <typename T>
 __device__ __forceinline__ float to_float(T v);
 template <>

@@ -73,7 +73,7 @@ __device__ __forceinline__ uint4 lds16(uint32_t addr) {
 template <int MT, int TILES, typename TOut>
 __global__ void __launch_bounds__(SW * 32, 1)
 gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, TOut* __restrict__ y, int M, int N,
-                   int K, int ldy, int up_offset, int act) {
+                   int K, int ldy, int up_offset, int act, GluClip clip) {
   using Shape = StreamShape<MT, TILES>;
   constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES;
   constexpr uint32_t STAGE_BYTES = PIECES * 32 * 16;
@@ -208,7 +208,7 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       if (TILES == 2) {
         const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
         const float up = __bfloat162float(__float2bfloat16_rn(v[TILES - 1]));
-        out = gate_act(gate, act) * up;
+        out = gated_value(gate, up, act, clip);
       } else {
         out = v[0];
       }
@@ -219,7 +219,8 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 }
 
 template <int MT, int TILES, typename TOut>
-int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, int act, int sms, cudaStream_t stream) {
+int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, int ldy, int up_offset, int act, int sms, cudaStream_t stream,
+                  const GluClip& clip = GluClip{}) {
   using Shape = StreamShape<MT, TILES>;
   static PsbPerDevice configured; 
   if (!configured.get()) {
@@ -231,7 +232,7 @@ int launch_stream(const void* x, const void* W, void* y, int M, int N, int K, in
   const int tiles = (N + 15) / 16;
   const int grid = tiles < sms ? tiles : sms;
   psb_launch(gemm_stream_kernel<MT, TILES, TOut>, dim3(grid), dim3(SW * 32), (size_t)Shape::SMEM_BYTES, stream,
-      (const __nv_bfloat16*)x, (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset, act);
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset, act, clip);
   return 0;
 }
 
@@ -259,6 +260,20 @@ PSB_API int psb_gemm_stream_gated(const void* x, const void* W, void* act, int M
                         : launch_stream<2, 2, __nv_bfloat16>(x, W, act, M, I, K, I, I, activation, sms, stream);
   if (rc) return rc;
   PSB_LAUNCH_CHECK("gemm_stream_gated");
+  return 0;
+}
+
+// The same with the clipped gate (see GluClip): both sums rounded to bfloat16, then clipped, then combined.
+PSB_API int psb_gemm_stream_gated_clipped(const void* x, const void* W, void* act, int M, int I, int K, int sms, float limit,
+                                          float alpha, float offset, cudaStream_t stream) {
+  if (!(limit > 0.f)) PSB_REFUSE("gemm_stream_gated_clipped: the limit must be positive");
+  if (M < 0 || M > 16 || I < 1 || K < 32 || K % 32 || sms < 1) PSB_REFUSE("gemm_stream_gated_clipped: needs M <= 16 and K a multiple of 32 (M=%d I=%d K=%d)", M, I, K);
+  if (M == 0) return 0;
+  const GluClip clip{limit, alpha, offset};
+  const int rc = M <= 8 ? launch_stream<1, 2, __nv_bfloat16>(x, W, act, M, I, K, I, I, PSB_ACT_CLIPPED, sms, stream, clip)
+                        : launch_stream<2, 2, __nv_bfloat16>(x, W, act, M, I, K, I, I, PSB_ACT_CLIPPED, sms, stream, clip);
+  if (rc) return rc;
+  PSB_LAUNCH_CHECK("gemm_stream_gated_clipped");
   return 0;
 }
 
@@ -308,7 +323,8 @@ template <int MT, int TILES, int CPW, typename TOut, bool ROPE = false>
 __global__ void __launch_bounds__(SW * 32, 1)
 gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __restrict__ pending, const float* __restrict__ gain,
                         const int32_t* __restrict__ rows, float* __restrict__ h_out, const __nv_bfloat16* __restrict__ W,
-                        TOut* __restrict__ y, int M, int N, int K, int ldy, int up_offset, int act, float eps, RopeArgs rope) {
+                        TOut* __restrict__ y, int M, int N, int K, int ldy, int up_offset, int act, float eps, RopeArgs rope,
+                        GluClip clip) {
   using Shape = NormStreamShape<MT, TILES>;
   constexpr int STAGES = Shape::STAGES, PIECES = Shape::PIECES;
   constexpr uint32_t STAGE_BYTES = PIECES * 32 * 16;
@@ -540,7 +556,7 @@ gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __r
       if (TILES == 2) {
         const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
         const float up = __bfloat162float(__float2bfloat16_rn(v[TILES - 1]));
-        out = gate_act(gate, act) * up;
+        out = gated_value(gate, up, act, clip);
       } else {
         out = v[0];
       }
@@ -554,7 +570,7 @@ gemm_stream_norm_kernel(const float* __restrict__ h_in, const __nv_bfloat16* __r
 template <int MT, int TILES, int CPW, typename TOut, bool ROPE = false>
 int launch_norm_stream(const void* h_in, const void* pending, const void* gain, const void* rows, void* h_out, const void* W,
                        void* y, int M, int N, int K, int ldy, int up_offset, int act, float eps, int sms, cudaStream_t stream,
-                       const RopeArgs& rope = RopeArgs{}) {
+                       const RopeArgs& rope = RopeArgs{}, const GluClip& clip = GluClip{}) {
   using Shape = NormStreamShape<MT, TILES>;
   static PsbPerDevice configured; 
   if (!configured.get()) {
@@ -567,15 +583,16 @@ int launch_norm_stream(const void* h_in, const void* pending, const void* gain, 
   const int grid = tiles < sms ? tiles : sms;
   psb_launch(gemm_stream_norm_kernel<MT, TILES, CPW, TOut, ROPE>, dim3(grid), dim3(SW * 32), (size_t)Shape::SMEM_BYTES, stream,
              (const float*)h_in, (const __nv_bfloat16*)pending, (const float*)gain, (const int32_t*)rows, (float*)h_out,
-             (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset, act, eps, rope);
+             (const __nv_bfloat16*)W, (TOut*)y, M, N, K, ldy, up_offset, act, eps, rope, clip);
   return 0;
 }
 
 template <int TILES, typename TOut>
 int dispatch_norm_stream(const void* h_in, const void* pending, const void* gain, const void* rows, void* h_out, const void* W,
-                         void* y, int M, int N, int K, int ldy, int up_offset, int act, float eps, int sms, cudaStream_t stream) {
+                         void* y, int M, int N, int K, int ldy, int up_offset, int act, float eps, int sms, cudaStream_t stream,
+                         const GluClip& clip = GluClip{}) {
   const int cpw = (K / 32 + SW - 1) / SW;  // the most chunks any warp owns
-#define PSB_NS(MT, CPW) launch_norm_stream<MT, TILES, CPW, TOut>(h_in, pending, gain, rows, h_out, W, y, M, N, K, ldy, up_offset, act, eps, sms, stream)
+#define PSB_NS(MT, CPW) launch_norm_stream<MT, TILES, CPW, TOut>(h_in, pending, gain, rows, h_out, W, y, M, N, K, ldy, up_offset, act, eps, sms, stream, RopeArgs{}, clip)
   if (M <= 8) {
     if (cpw <= 4) return PSB_NS(1, 4);
     if (cpw <= 8) return PSB_NS(1, 8);
@@ -637,6 +654,19 @@ PSB_API int psb_gemm_stream_norm_gated(const void* h_in, const void* pending, co
   if (!(eps > 0.f)) PSB_REFUSE("gemm_stream_norm_gated: eps must be positive");
   if (int rc = dispatch_norm_stream<2, __nv_bfloat16>(h_in, pending, gain, nullptr, h_out, W, act, M, I, K, I, I, activation, eps, sms, stream)) return rc;
   PSB_LAUNCH_CHECK("gemm_stream_norm_gated");
+  return 0;
+}
+
+// The same with the clipped gate (see GluClip).
+PSB_API int psb_gemm_stream_norm_gated_clipped(const void* h_in, const void* pending, const void* gain, void* h_out, const void* W,
+                                               void* act, int M, int I, int K, float eps, int sms, float limit, float alpha,
+                                               float offset, cudaStream_t stream) {
+  if (!(limit > 0.f)) PSB_REFUSE("gemm_stream_norm_gated_clipped: the limit must be positive");
+  if (!psb_gemm_stream_norm_supported(M, K) || I < 1 || sms < 1) PSB_REFUSE("gemm_stream_norm_gated_clipped: shape M=%d I=%d K=%d is not taken", M, I, K);
+  if (!(eps > 0.f)) PSB_REFUSE("gemm_stream_norm_gated_clipped: eps must be positive");
+  if (int rc = dispatch_norm_stream<2, __nv_bfloat16>(h_in, pending, gain, nullptr, h_out, W, act, M, I, K, I, I, PSB_ACT_CLIPPED, eps, sms,
+                                                      stream, GluClip{limit, alpha, offset})) return rc;
+  PSB_LAUNCH_CHECK("gemm_stream_norm_gated_clipped");
   return 0;
 }
 

@@ -70,16 +70,10 @@ using namespace tc;
 // 0; the epilogue rotates queries and keys and stores queries, keys and values where RopeArgs says, C is not used).
 enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_ROPE = 2, MODE_GATED_GELU = 3, MODE_RELU2 = 4, MODE_GATED_CLIPPED = 5 };
 // gated: SiLU, the tanh form of GELU, or (clipped) g * sigmoid(alpha g) * (u + offset) with g = min(gate, limit) and
-// u = clamp(up, -limit, limit), the three numbers in GluArgs.
-struct GluArgs {
-  float limit, alpha, offset;
-};
+// u = clamp(up, -limit, limit), the three numbers in a GluClip (common.cuh).
+using GluArgs = GluClip;
 __device__ __forceinline__ bool mode_is_gated(int mode) { return mode == MODE_GATED || mode == MODE_GATED_GELU || mode == MODE_GATED_CLIPPED; }
-__device__ __forceinline__ float clipped_gate(float g, float u, const GluArgs& a) {
-  g = fminf(g, a.limit);
-  u = fminf(fmaxf(u, -a.limit), a.limit);
-  return g / (1.f + expf(-a.alpha * g)) * (u + a.offset);
-}
+__device__ __forceinline__ float clipped_gate(float g, float u, const GluArgs& a) { return clipped_gate_value(g, u, a); }
 // MODE_RELU2: columns as in 0, the epilogue stores max(sum, 0)^2.
 //
 // Grouped products (``tile_expert`` given): W is a stack of matrices [experts * N_out, K] and every 128-row tile of A

@@ -1103,11 +1103,19 @@ CLIPPED_FUSED_MIN_ROWS = 65  # from here on no product folds the norm in front o
 
 def clipped_gated_linear(x, w_gate_up: torch.Tensor, limit: float, alpha: float = 1.702, offset: float = 1.0) -> torch.Tensor:
     """g * sigmoid(alpha g) * (u + offset) with g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit) for W = [gate rows;
-    up rows]: many bfloat16 rows in the product's epilogue, else product (which may fold the norm in front into itself)
-    and then the activation.  Both ways round the two products to the compute type before they are clipped."""
-    if x.shape[0] >= CLIPPED_FUSED_MIN_ROWS and x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16:
+    up rows].  bfloat16: a few rows in the streaming product's epilogue (with the norm in front, if ``x`` still carries
+    it), many in the tcgen05 product's; between the two, and in float32, product (which may fold the norm in front
+    into itself) and then the activation.  Every way rounds the two products to the compute type before they are clipped."""
+    both16 = x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
+    if both16 and isinstance(x, NormedRows) and x.fusable:   # few rows: the norm in front, both products and the gate in one kernel
+        from .tensorcore import norm_gated_linear_bf16
+        act = norm_gated_linear_bf16(x, w_gate_up, clip=(limit, alpha, offset))
+        if act is not None:
+            return act
+    if both16 and (x.shape[0] >= CLIPPED_FUSED_MIN_ROWS or not isinstance(x, NormedRows)):
         from .tensorcore import clipped_gated_linear_bf16
         rows = x.tensor() if isinstance(x, NormedRows) else x
+        _dev(rows, "left operand"), _dev(w_gate_up, "weight")
         act = clipped_gated_linear_bf16(rows, w_gate_up, limit, alpha, offset)
         if act is not None:
             return act

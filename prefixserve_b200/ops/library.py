@@ -86,6 +86,10 @@ _SIGNATURES: dict[str, list] = {
     "psb_gemm_tcgen05_gated": [P, P, P, I, I, I, I, I, P],
     # (a, w, act, M, I, K, sms, limit, alpha, offset, stream)
     "psb_gemm_tcgen05_gated_clipped": [P, P, P, I, I, I, I, F, F, F, P],
+    # (x, W, act, M, I, K, sms, limit, alpha, offset, stream)
+    "psb_gemm_stream_gated_clipped": [P, P, P, I, I, I, I, F, F, F, P],
+    # (h_in, pending, gain, h_out, W, act, M, I, K, eps, sms, limit, alpha, offset, stream)
+    "psb_gemm_stream_norm_gated_clipped": [P, P, P, P, P, P, I, I, I, F, I, F, F, F, P],
     "psb_gemm_tcgen05_tile_width": [I],
     # (M, N_out, kind, D, sms) -> output tiles at the width the kernel would choose
     "psb_gemm_tcgen05_tiles": [I, I, I, I, I],

@@ -76,10 +76,15 @@ def gemm_stream(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> tor
     return y
 
 
-def gemm_stream_gated(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int = 0) -> torch.Tensor:
+def gemm_stream_gated(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int = 0, clip: tuple | None = None) -> torch.Tensor:
+    """``clip`` (limit, alpha, offset): the clipped gate instead of the activation named by its code."""
     m, k = x.shape
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
+    if clip is not None:
+        check(lib().psb_gemm_stream_gated_clipped(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, _sms(x.device),
+                                                  float(clip[0]), float(clip[1]), float(clip[2]), stream_handle()), "gemm_stream_gated_clipped")
+        return act
     check(lib().psb_gemm_stream_gated(x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), m, inter, k, _sms(x.device),
                                       activation, stream_handle()), "gemm_stream_gated")
     return act
@@ -138,14 +143,22 @@ def norm_qkv_rope_bf16(x, w_qkv, positions, token_item, cos, sin, table, kv, hq,
     return q
 
 
-def norm_gated_linear_bf16(x, w_gate_up: torch.Tensor, activation: int = 0) -> torch.Tensor | None:
-    """act(x Wg^T) * (x Wu^T) with x = rmsnorm(h + pending), all in the streaming kernel; None when it does not fit."""
+def norm_gated_linear_bf16(x, w_gate_up: torch.Tensor, activation: int = 0, clip: tuple | None = None) -> torch.Tensor | None:
+    """act(x Wg^T) * (x Wu^T) with x = rmsnorm(h + pending), all in the streaming kernel; None when it does not fit.
+    ``clip`` (limit, alpha, offset): the clipped gate instead of the activation named by its code."""
     if w_gate_up.shape[0] % 2 or x.rows is not None or not _norm_fusable(x, w_gate_up):
         return None
     m, k = x.shape
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((m, inter), dtype=torch.bfloat16, device=w_gate_up.device)
     new_h = torch.empty_like(x.h) if x.pending is not None else None
+    if clip is not None:
+        check(lib().psb_gemm_stream_norm_gated_clipped(x.h.data_ptr(), None if x.pending is None else x.pending.data_ptr(), x.gain.data_ptr(),
+                                                       None if new_h is None else new_h.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(),
+                                                       m, inter, k, x.eps, _sms(w_gate_up.device), float(clip[0]), float(clip[1]),
+                                                       float(clip[2]), stream_handle()), "gemm_stream_norm_gated_clipped")
+        x.fused(new_h)
+        return act
     check(lib().psb_gemm_stream_norm_gated(x.h.data_ptr(), None if x.pending is None else x.pending.data_ptr(), x.gain.data_ptr(),
                                            None if new_h is None else new_h.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(),
                                            m, inter, k, x.eps, _sms(w_gate_up.device), activation,
@@ -279,9 +292,13 @@ def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor, activation: int
 
 def clipped_gated_linear_bf16(x: torch.Tensor, w_gate_up: torch.Tensor, limit: float, alpha: float, offset: float) -> torch.Tensor | None:
     """g * sigmoid(alpha g) * (u + offset) with g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit), in the epilogue
-    of the tcgen05 product; None when that kernel does not take the shape (few rows, sizes)."""
+    of the streaming product (few rows) or of the tcgen05 product (many); None when neither takes the shape."""
     m, k = x.shape
-    if w_gate_up.shape[0] % 2 or m <= STREAM_M or not _tcgen05_ok(x, w_gate_up, 1):
+    if w_gate_up.shape[0] % 2 or not (x.is_contiguous() and w_gate_up.is_contiguous()):
+        return None
+    if small_m_ok(m, k, min(STREAM_M, 16)):
+        return gemm_stream_gated(x, w_gate_up, clip=(limit, alpha, offset))
+    if m <= STREAM_M or not _tcgen05_ok(x, w_gate_up, 1):
         return None
     inter = w_gate_up.shape[0] // 2
     act = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)

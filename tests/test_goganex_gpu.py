@@ -492,10 +492,11 @@ def test_clipped_gate_alone(dtype):
         assert torch.allclose(got, want, atol=1e-5 if dtype == torch.float32 else 3e-2, rtol=0 if dtype == torch.float32 else 1e-2)
 
 
-@pytest.mark.parametrize("rows", [40, 1024])
+@pytest.mark.parametrize("rows", [5, 40, 1024])
 def test_clipped_gated_product_alone(rows):
-    """Both products and the clipped gate as one op (many bfloat16 rows: in the product's epilogue; few: product, then
-    gate) against the plain feed-forward with an identity behind it."""
+    """Both products and the clipped gate as one op (a few bfloat16 rows: in the streaming product's epilogue, also with
+    the norm in front; many: in the tcgen05 product's; between: product, then gate) against the plain feed-forward
+    with an identity behind it."""
     from prefixserve_b200 import ops
     g = torch.Generator().manual_seed(rows)
     width, ff = 256, 2048
@@ -506,6 +507,15 @@ def test_clipped_gated_product_alone(rows):
         got = ops.clipped_gated_linear(x.cuda(), w.cuda(), limit).cpu().double()
         want = plain.feed_forward({"limit": limit}, {"f.gate": w[:ff].double(), "f.up": w[ff:].double(), "f.down": eye}, "f.", x.double())
         assert got.shape == want.shape and torch.allclose(got, want, atol=4e-2, rtol=2e-2)
+    # the same behind a norm that has not run yet: stream + delta, norm, products, gate
+    h, delta = torch.randn(rows, width, generator=g), torch.randn(rows, width, generator=g).to(torch.bfloat16)
+    gain = 1 + 0.1 * torch.randn(width, generator=g)
+    x = ops.NormedRows(h.cuda(), delta.cuda(), gain.cuda(), 1e-5, torch.bfloat16)
+    got = ops.clipped_gated_linear(x, w.cuda(), 1.5).cpu().double()
+    normed = plain.norm(h.double() + delta.double(), gain.double(), 1e-5)
+    want = plain.feed_forward({"limit": 1.5}, {"f.gate": w[:ff].double(), "f.up": w[ff:].double(), "f.down": eye}, "f.", normed)
+    assert torch.allclose(got, want, atol=5e-2, rtol=2e-2)
+    assert torch.allclose(x.residual().cpu().double(), h.double() + delta.double(), atol=1e-6)
 
 
 # ---- generation through the scheduler --------------------------------------------------------------------------
