@@ -95,10 +95,12 @@ def test_every_cutting_matches_the_plain_model(made, which, dtype, trace):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("page_size", [1, 4, 64])
-def test_token_by_token_through_small_and_large_pages(made, dtype, page_size):
-    """Every token decoded alone from the first on, over many page borders: prefill against token-by-token decoding."""
-    folder, truth = made["mixed", dtype]
-    seqs = {rid: toks for rid, toks in sequences(131).items() if len(toks) in (2, 140)}
+@pytest.mark.parametrize("which", ["mixed", "planes"])
+def test_token_by_token_through_small_and_large_pages(made, which, dtype, page_size):
+    """Every token decoded alone from the first on, over many page borders: prefill against token-by-token decoding.
+    (Pages below 16 tokens take the plane layout to the attention kernel that walks its keys.)"""
+    folder, truth = made[which, dtype]
+    seqs = {rid: toks for rid, toks in sequences(gm.CONFIGS[which]["vocab"]).items() if len(toks) in (2, 140)}
     steps = helpers.trace_tail_decode(seqs, tail=10 ** 6)
     rows = replay(folder, dtype, steps, page_size=page_size, max_tokens=helpers.peak_tokens(steps, page=max(page_size, 64)))
     assert worst_error(rows, truth) < LIMIT[dtype]
