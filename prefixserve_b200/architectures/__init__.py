@@ -1,3 +1,3 @@
 """Importing this package registers every architecture the engine ships."""
 
-from . import gekopel, goganex, llama, nerenex  # noqa: F401
+from . import gekopel, goganex, llama, nerenex, zomolix  # noqa: F401

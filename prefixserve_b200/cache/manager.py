@@ -55,9 +55,10 @@ class _Group:
     tables: SeqTables
     entries: list[int]
     chunk: int | None = None  # keys before the current run of ``chunk`` positions are out of reach
+    keep_first: int = 0       # with a window: the first so many keys stay readable, their pages are never given back early
 
     def lowest_key(self, position: int) -> int:
-        """The lowest key position a query at ``position`` or later can still read."""
+        """The lowest key position a query at ``position`` or later can still read (the kept first keys aside)."""
         low = 0
         if self.window is not None:
             low = max(low, position - self.window + 1)
@@ -93,19 +94,20 @@ class CacheManager:
         # group entries by window
         self.groups: list[_Group] = []
         self.entry_group: list[int | None] = []
-        by_window: dict[tuple[int | None, int | None], int] = {}
+        by_window: dict[tuple[int | None, int | None, int], int] = {}
         for i, need in enumerate(self.needs):
             if need.paged is None:
                 self.entry_group.append(None)
                 continue
             w, c = need.paged.window, need.paged.chunk
-            if (w is not None and w < 1) or (c is not None and c < 1):
-                raise ValueError(f"cache entry {i}: window {w} and chunk {c} must be >= 1")
-            if (w, c) not in by_window:
-                by_window[(w, c)] = len(self.groups)
+            k = int(need.paged.keep_first or 0) if w is not None else 0
+            if (w is not None and w < 1) or (c is not None and c < 1) or k < 0:
+                raise ValueError(f"cache entry {i}: window {w} and chunk {c} must be >= 1, kept first keys {k} >= 0")
+            if (w, c, k) not in by_window:
+                by_window[(w, c, k)] = len(self.groups)
                 n = num_pages[len(self.groups)] if isinstance(num_pages, Mapping) else int(num_pages)
-                self.groups.append(_Group(w, BlockManager(n), SeqTables(num_slots, self.max_pages_per_seq), [], c))
-            g = by_window[(w, c)]
+                self.groups.append(_Group(w, BlockManager(n), SeqTables(num_slots, self.max_pages_per_seq), [], c, k))
+            g = by_window[(w, c, k)]
             self.groups[g].entries.append(i)
             self.entry_group.append(g)
 
@@ -189,6 +191,9 @@ class CacheManager:
         for n in needs:
             if n.paged is not None:
                 key = n.paged.window if n.paged.chunk is None else ("chunk", n.paged.chunk, n.paged.window)
+                if n.paged.window is not None and n.paged.keep_first:
+                    # a window that also keeps a sequence's first keys: both, and the page the kept keys end in
+                    key = ("kept", n.paged.window + n.paged.keep_first + page_size, n.paged.window, n.paged.keep_first)
                 out[key] = out.get(key, 0) + n.paged.planes * n.paged.num_kv_heads * page_size * n.paged.head_dim * item
         return out
 
@@ -196,6 +201,8 @@ class CacheManager:
     def reach_tokens(reach) -> int | None:
         """The most keys a query of a group with this reach (a key of ``group_page_bytes``) can read; None: all."""
         if isinstance(reach, tuple):
+            if reach[0] == "kept":
+                return reach[1]
             return min(x for x in reach[1:] if x is not None)
         return reach
 
@@ -322,7 +329,7 @@ class CacheManager:
         for g in self.groups:
             if g.window is None and g.chunk is None:
                 continue
-            ids = g.tables.release_front(slot, self._first_needed_page(g, computed))
+            ids = g.tables.release_front(slot, self._first_needed_page(g, computed), pages_for(g.keep_first, self.page_size))
             if ids:
                 g.pool.decref_many(ids)
                 self._poison(g, ids)

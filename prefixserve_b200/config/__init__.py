@@ -1,6 +1,7 @@
 from .llama import Llama3RopeScaling, LlamaConfig, UnsupportedModelError
 from .gekopel import BiasedAttentionConfig, DeltaConfig, DenseFF, GekopelConfig, GekopelLayer, RoutedFF
 from .goganex import AttentionConfig, ClippedFF, GoganexConfig, GoganexLayer, ParallelConfig, RotationConfig
+from .zomolix import ZomolixConfig, ZomolixLayer
 from .nerenex import LatentAttentionConfig, NerenexConfig, NerenexLayer, RecurrentConfig
 from .registry import (
     Architecture,
@@ -15,7 +16,7 @@ from .spec import LayerCall, LayerSpec, ModelSpec, PartSpec, part, sequential_sc
 
 __all__ = [
     "Architecture", "AttentionConfig", "ClippedFF", "GoganexConfig", "GoganexLayer", "ParallelConfig", "RotationConfig", "BiasedAttentionConfig", "DeltaConfig", "DenseFF", "GekopelConfig", "GekopelLayer", "RoutedFF", "LatentAttentionConfig", "LayerCall", "LayerSpec", "Llama3RopeScaling", "LlamaConfig", "ModelSpec",
-    "NerenexConfig", "NerenexLayer", "PartSpec", "RecurrentConfig",
+    "NerenexConfig", "NerenexLayer", "ZomolixConfig", "ZomolixLayer", "PartSpec", "RecurrentConfig",
     "UnknownArchitectureError", "UnsupportedModelError", "architecture_of", "get_architecture", "part",
     "read_model_folder", "register_architecture", "registered_architectures", "sequential_schedule",
 ]

@@ -64,6 +64,10 @@ class LayerSpec:
     # For arrangements with a norm on both sides of a sublayer ("sandwich_norm"): the norms of the sublayers' results.
     mixer_post_norm: PartSpec | None = None
     ffn_post_norm: PartSpec | None = None
+    # For the "pre_norm" arrangement: a learned factor per channel on the mixer's and on the feed-forward's result
+    # before it joins the stream (a gate of kind "channel_scale"; None: the result joins as it is).
+    mixer_scale: PartSpec | None = None
+    ffn_scale: PartSpec | None = None
 
     def __post_init__(self) -> None:
         if (self.ffn is None) != (self.ffn_norm is None):

@@ -225,13 +225,15 @@ PYBIND11_MODULE(_core, m) {
            },
            py::arg("slot"), py::arg("block_ids"))
       .def("release_front",
-           [](SeqTables& t, int64_t s, int64_t upto) {
+           [](SeqTables& t, int64_t s, int64_t upto, int64_t keep) {
              if (!t.slot_ok(static_cast<int32_t>(s))) throw py::value_error("slot out of range");
+             if (keep < 0) throw py::value_error("keep must be >= 0");
              std::vector<PageId> out(static_cast<size_t>(t.max_pages()));
-             const int32_t n = t.release_front(static_cast<int32_t>(s), static_cast<int32_t>(std::max<int64_t>(upto, 0)), out.data());
+             const int32_t n = t.release_front(static_cast<int32_t>(s), static_cast<int32_t>(std::max<int64_t>(upto, 0)), out.data(),
+                                               static_cast<int32_t>(std::min<int64_t>(keep, t.max_pages())));
              return to_list(out, static_cast<size_t>(n));
            },
-           py::arg("slot"), py::arg("upto_page"))
+           py::arg("slot"), py::arg("upto_page"), py::arg("keep") = 0)
       .def("clear",
            [](SeqTables& t, int64_t s) {
              if (!t.slot_ok(static_cast<int32_t>(s))) throw py::value_error("slot out of range");

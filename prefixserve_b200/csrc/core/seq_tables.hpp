@@ -183,12 +183,18 @@ class SeqTables {
     return true;
   }
 
-  // Takes the live entries with index < upto out of the row (they become
-  // kNoPage) and writes them to out; returns how many.
-  int32_t release_front(int32_t s, int32_t upto, PageId* out) noexcept {
+  // Takes the live entries with index in [keep, upto) out of the row (they
+  // become kNoPage) and writes them to out; returns how many.  ``keep``: the
+  // row's first entries that stay whatever upto says (a mask that lets every
+  // query read a sequence's first keys); 0 for a plain window.
+  int32_t release_front(int32_t s, int32_t upto, PageId* out, int32_t keep = 0) noexcept {
     int32_t& b = begin_[static_cast<size_t>(s)];
     const int32_t e = end_[static_cast<size_t>(s)];
     if (upto > e) upto = e;
+    if (keep > 0 && b < keep) {
+      if (upto <= keep) return 0;  // nothing beyond the kept entries is out of reach yet
+      b = keep;
+    }
     PageId* r = row(s);
     int32_t n = 0;
     for (; b < upto; ++b) {
@@ -198,8 +204,9 @@ class SeqTables {
     return n;
   }
 
-  // Empties the row; the live ids go to out.
+  // Empties the row, kept entries included; the live ids go to out.
   int32_t clear(int32_t s, PageId* out) noexcept {
+    begin_[static_cast<size_t>(s)] = 0;
     const int32_t n = release_front(s, end_[static_cast<size_t>(s)], out);
     begin_[static_cast<size_t>(s)] = 0;
     end_[static_cast<size_t>(s)] = 0;

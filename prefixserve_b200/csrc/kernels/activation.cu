@@ -68,7 +68,31 @@ __global__ void unary_act_vec_kernel(const __nv_bfloat16* __restrict__ x, __nv_b
   }
 }
 
+// out = x * gate, element by element: gate float32 (a sigmoid that somebody has already taken), the product in float32
+template <typename TX, typename TO>
+__global__ void gate_mul_kernel(const TX* __restrict__ x, const float* __restrict__ gate, TO* __restrict__ out, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_float<TO>(to_float<TX>(x[i]) * gate[i]);
+}
+
 }  // namespace
+
+// (x, x_dtype, gate float32, out, out_dtype, total, stream)
+PSB_API int psb_gate_mul(const void* x, int x_dtype, const void* gate, void* out, int out_dtype, long long total, cudaStream_t stream) {
+  if (total < 0) PSB_REFUSE("gate_mul: negative size");
+  if (total == 0) return 0;
+  const long long blocks = (total + 255) / 256;
+  PSB_DISPATCH_DTYPE(x_dtype, TX, {
+    PSB_DISPATCH_DTYPE(out_dtype, TO, {
+      psb_launch(gate_mul_kernel<TX, TO>, dim3((unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks)), dim3(256), 0, stream,
+                 (const TX*)x, (const float*)gate, (TO*)out, (size_t)total);
+    });
+  });
+  PSB_LAUNCH_CHECK("gate_mul");
+  return 0;
+}
 
 PSB_API int psb_unary_act(const void* x, int dtype, void* out, long long total, int code, const void* params,
                           cudaStream_t stream) {

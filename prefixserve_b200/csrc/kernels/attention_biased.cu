@@ -1,7 +1,9 @@
 // Causal grouped-query attention over the paged cache for designs whose scores carry more than q.k:
 //
 //   score(i, j) = (q_i . k_j) * scale + bias[h][min(i - j, reach - 1)]       (bias optional)
-//   visible:  j <= i,  j > i - window (window optional),  floor(j / chunk) == floor(i / chunk) (chunk optional)
+//   visible:  j <= i,  j > i - window (window optional),  floor(j / chunk) == floor(i / chunk) (chunk optional);
+//             with ``keep_first`` > 0 (and a window, no chunk) the first keep_first keys of the sequence stay visible
+//             to every later query, at their true positions: j <= i and (j > i - window or j < keep_first)
 //   weights = exp(score) / (sum over visible j of exp(score) + exp(sink[h]))  (sink optional: a term of the
 //             denominator that has no key and no value)
 //
@@ -106,7 +108,7 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
                         int table_width, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_item,
                         const float* __restrict__ bias, const float* __restrict__ sink, T* __restrict__ out, int T_tokens,
                         int hq, int hkv, int dim, int vdim, int page_size, int window, int chunk, int reach, float scale,
-                        const int32_t* __restrict__ item_start, int skip_from) {
+                        const int32_t* __restrict__ item_start, int skip_from, int keep_first) {
   __shared__ __align__(16) float qs[MAX_D];
   __shared__ float part[WARPS][MAX_D + 2];
   pdl_trigger();
@@ -124,6 +126,13 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
 
   int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   if (chunk > 0) lo = max(lo, (p / chunk) * chunk);
+  // kept first keys: when the window still reaches them the visible keys are one stretch from 0; otherwise their runs
+  // (counted from key 0) come before the window's runs, and the keys between the two are never touched
+  int kept_runs = 0;
+  if (keep_first > 0) {
+    if (lo <= keep_first) lo = 0;
+    else kept_runs = (keep_first + 31) >> 5;
+  }
   const int rw = dim + vdim;
   const size_t head_stride = (size_t)page_size * rw;
   const size_t page_elems = (size_t)hkv * head_stride;
@@ -136,9 +145,12 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
 #pragma unroll
   for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
 
-  for (int base = (lo & ~31) + 32 * warp; base <= p; base += 32 * WARPS) {
+  for (int run = warp;; run += WARPS) {
+    const bool kept = run < kept_runs;
+    const int base = kept ? 32 * run : (lo & ~31) + 32 * (run - kept_runs);
+    if (base > p) break;
     const int key = base + lane;
-    const bool live = key >= lo && key <= p;
+    const bool live = kept ? key < keep_first : (key >= lo && key <= p);
     long long off = -1;
     float s = -FLT_MAX;
     if (live) {
@@ -154,7 +166,7 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
     m = m_new;
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= alpha;
-    const int n_live = min(32, p - base + 1);
+    const int n_live = kept ? min(32, keep_first - base) : min(32, p - base + 1);
     // eight keys at a time: their value rows are asked for together, then added in key order
     for (int j0 = 0; j0 < n_live; j0 += 8) {
       float pj[8];
@@ -224,7 +236,7 @@ attention_biased_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
                              const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ positions,
                              const int32_t* __restrict__ item_start, int items, int min_tokens, const float* __restrict__ bias,
                              const float* __restrict__ sink, __nv_bfloat16* __restrict__ out, int hq, int hkv, int dim, int vdim,
-                             int page_size, int window, int chunk, int reach, float scale) {
+                             int page_size, int window, int chunk, int reach, float scale, int keep_first) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
@@ -265,7 +277,17 @@ attention_biased_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   }
   int lo_tile = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
   if (chunk > 0) lo_tile = max(lo_tile, (p_first / chunk) * chunk);
-  for (int base = lo_tile & ~31; base <= p_last; base += 32) {
+  // kept first keys: one stretch from 0 while the tile's first token still reaches them; else their runs come first
+  // (then every token of the tile has a gap between the kept keys and its window)
+  int kept_runs = 0;
+  if (keep_first > 0) {
+    if (lo_tile <= keep_first) lo_tile = 0;
+    else kept_runs = (keep_first + 31) >> 5;
+  }
+  for (int run = 0;; ++run) {
+    const bool kept = run < kept_runs;
+    const int base = kept ? 32 * run : (lo_tile & ~31) + 32 * (run - kept_runs);
+    if (base > p_last) break;
     __syncthreads();
     // stage the run: keys transposed, values as rows; a key beyond the tile's last position is left as zeros
     for (int i = threadIdx.x; i < 32 * (DP + VP) / 2; i += blockDim.x) {
@@ -275,7 +297,7 @@ attention_biased_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
       const bool is_key = e < DP;
       const int col = is_key ? e : e - DP;
       const int width = is_key ? dim : vdim;
-      if (key >= lo_tile && key <= p_last && col < width) {
+      if ((kept ? key < keep_first : (key >= lo_tile && key <= p_last)) && col < width) {
         const int page = pages[key / page_size];
         const __nv_bfloat16* src = kv + (size_t)page * page_elems + (size_t)g * head_stride + (size_t)(key % page_size) * rw +
                                    (is_key ? 0 : dim) + col;
@@ -292,9 +314,12 @@ attention_biased_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
       if (base > p) continue;
       int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
       if (chunk > 0) lo = max(lo, (p / chunk) * chunk);
-      if (base + 31 < lo) continue;
+      if (keep_first > 0 && lo <= keep_first) lo = 0;
+      // (a tile whose first token still reaches the kept keys has no kept runs, but a later token's window may
+      // already start beyond them: such a token sees the kept keys inside the ordinary runs)
+      if (!kept && base + 31 < lo && base >= keep_first) continue;
       const int key = base + lane;
-      const bool live = key >= lo && key <= p;
+      const bool live = kept ? key < keep_first : (key <= p && (key >= lo || key < keep_first));
       float s = -FLT_MAX;
       if (live) {
         const float* qq = qs + (size_t)u * DP;
@@ -314,8 +339,8 @@ attention_biased_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
       float a[VP / 32];
 #pragma unroll
       for (int i = 0; i < VP / 32; ++i) a[i] = acc[lane + 32 * i] * alpha;
-      const int n_live = min(32, p - base + 1);
-      const int j0 = max(0, lo - base);
+      const int n_live = kept ? min(32, keep_first - base) : min(32, p - base + 1);
+      const int j0 = (kept || base < keep_first) ? 0 : max(0, lo - base);
       for (int j = j0; j < n_live; ++j) {
         const float pj = __shfl_sync(0xffffffffu, pr, j);
 #pragma unroll
@@ -364,7 +389,7 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                             const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ positions,
                             const int32_t* __restrict__ item_start, int items, int min_tokens, const float* __restrict__ bias,
                             const float* __restrict__ sink, __nv_bfloat16* __restrict__ out, int hq, int hkv, int dim, int vdim,
-                            int page_size, int window, int chunk, int reach, float scale) {
+                            int page_size, int window, int chunk, int reach, float scale, int keep_first) {
   constexpr int KS = D + 8, VS = MMA_KEYS + 8;  // row pitches that keep the fragment loads off each other's banks
   __shared__ __align__(16) __nv_bfloat16 ks[MMA_KEYS * KS];   // keys [key][d]; first the tile's queries [row][d]
   __shared__ __align__(16) __nv_bfloat16 vt[V * VS];          // values transposed [v][key]
@@ -411,6 +436,7 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     pos[r] = p_first + warp * 16 + gid + 8 * r;
     low[r] = (window > 0 && pos[r] - window + 1 > 0) ? pos[r] - window + 1 : 0;
     if (chunk > 0) low[r] = max(low[r], (pos[r] / chunk) * chunk);
+    if (keep_first > 0 && low[r] <= keep_first) low[r] = 0;
     m[r] = sink ? sink[h] : -FLT_MAX;
     l[r] = (sink && tig == 0) ? 1.f : 0.f;
   }
@@ -423,7 +449,16 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
 
   int lo_tile = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
   if (chunk > 0) lo_tile = max(lo_tile, (p_first / chunk) * chunk);
-  for (int base = lo_tile & ~(MMA_KEYS - 1); base <= p_last; base += MMA_KEYS) {
+  // kept first keys: one stretch from 0 while the tile's first token still reaches them; else their blocks come first
+  int kept_blocks = 0;
+  if (keep_first > 0) {
+    if (lo_tile <= keep_first) lo_tile = 0;
+    else kept_blocks = (keep_first + MMA_KEYS - 1) / MMA_KEYS;
+  }
+  for (int blk = 0;; ++blk) {
+    const bool kept = blk < kept_blocks;
+    const int base = kept ? MMA_KEYS * blk : (lo_tile & ~(MMA_KEYS - 1)) + MMA_KEYS * (blk - kept_blocks);
+    if (base > p_last) break;
     __syncthreads();  // everybody has its query fragments (first round) or is done with the last block
     // every thread asks for all its pieces of the block (page ids first, then the rows) before it stores any
     constexpr int KPIECES = MMA_KEYS * (D / 8) / 128, VPIECES = MMA_KEYS * (V / 8) / 128;
@@ -434,7 +469,7 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
       const int j = i / (D / 8), c = (i - j * (D / 8)) * 8;
       const int key = base + j;
       kreg[u] = make_uint4(0, 0, 0, 0);
-      if (key >= lo_tile && key <= p_last && c < dim)
+      if ((kept ? key < keep_first : (key >= lo_tile && key <= p_last)) && c < dim)
         kreg[u] = *reinterpret_cast<const uint4*>(kv + (size_t)pages[key / page_size] * page_elems + (size_t)g * head_stride +
                                                   (size_t)(key % page_size) * rw + c);
     }
@@ -444,7 +479,7 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
       const int j = i % MMA_KEYS, c = (i / MMA_KEYS) * 8;  // neighbouring lanes: neighbouring keys, the same eight value channels
       const int key = base + j;
       vreg[u] = make_uint4(0, 0, 0, 0);
-      if (key >= lo_tile && key <= p_last && c < vdim)
+      if ((kept ? key < keep_first : (key >= lo_tile && key <= p_last)) && c < vdim)
         vreg[u] = *reinterpret_cast<const uint4*>(kv + (size_t)pages[key / page_size] * page_elems + (size_t)g * head_stride +
                                                   (size_t)(key % page_size) * rw + dim + c);
     }
@@ -464,6 +499,7 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     }
     __syncthreads();
     if (warp * 16 >= nt || base > p_first + warp * 16 + 15) continue;  // no rows, or all of them before the block (uniform in the warp)
+    // (a kept block lies before every row of a tile that has any: then every row's window starts beyond keep_first)
     float sc[MMA_KEYS / 8][4];
 #pragma unroll
     for (int n = 0; n < MMA_KEYS / 8; ++n) {
@@ -482,7 +518,7 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1, key = base + n * 8 + 2 * tig + (e & 1);
         float v = -INFINITY;
-        if (key <= pos[r] && key >= low[r]) {
+        if (kept ? key < keep_first : (key <= pos[r] && (key >= low[r] || key < keep_first))) {
           v = sc[n][e] * scale;
           if (brow) {
             const int far = min(pos[r] - key, reach - 1);
@@ -585,11 +621,12 @@ PSB_API int psb_attention_biased_append(const void* qkv, int dtype, const void* 
 
 // ``skip_from`` > 0: tokens of portions with at least that many tokens are left to the tiled kernel (item_start needed).
 // (q, dtype, kv, kv_dtype, table, table_width, positions, token_item, bias, sink, out, T, hq, hkv, dim, vdim, page_size,
-//  window, chunk, reach, scale, item_start, skip_from, stream)
+//  window, chunk, reach, scale, item_start, skip_from, keep_first, stream)
 PSB_API int psb_attention_biased(const void* q, int dtype, const void* kv, int kv_dtype, const void* table, int table_width,
                                  const void* positions, const void* token_item, const void* bias, const void* sink, void* out,
                                  int T, int hq, int hkv, int dim, int vdim, int page_size, int window, int chunk, int reach,
-                                 float scale, const void* item_start, int skip_from, cudaStream_t stream) {
+                                 float scale, const void* item_start, int skip_from, int keep_first, cudaStream_t stream) {
+  if (keep_first < 0 || (keep_first > 0 && (window < 1 || chunk > 0))) PSB_REFUSE("attention_biased: kept first keys go with a window and no chunk mask");
   if (skip_from > 0 && !item_start) PSB_REFUSE("attention_biased: skipping tiled portions needs the item offsets");
   if (T < 0 || hq < 1 || hkv < 1 || hq % hkv) PSB_REFUSE("attention_biased: %d query heads cannot share %d key/value heads", hq, hkv);
   if (dim < 1 || dim > MAX_D || vdim < 1 || vdim > MAX_D) PSB_REFUSE("attention_biased: sizes %d/%d are outside [1, %d]", dim, vdim, MAX_D);
@@ -603,7 +640,7 @@ PSB_API int psb_attention_biased(const void* q, int dtype, const void* kv, int k
       psb_launch(attention_biased_kernel<T_, TKV>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, (const T_*)q,
                  (const TKV*)kv, (const int32_t*)table, table_width, (const int32_t*)positions, (const int32_t*)token_item,
                  (const float*)bias, (const float*)sink, (T_*)out, T, hq, hkv, dim, vdim, page_size, window, chunk, reach, scale,
-                 (const int32_t*)item_start, skip_from);
+                 (const int32_t*)item_start, skip_from, keep_first);
     });
   });
   PSB_LAUNCH_CHECK("attention_biased");
@@ -618,12 +655,13 @@ PSB_API int psb_attention_biased_mma_supported(int hq, int hkv, int dim, int vdi
 // The tensor-core kernel over every portion of at least ``min_tokens`` tokens (bfloat16; grid sized by an upper bound on
 // the 64-token tiles).  Other tokens are left untouched.
 // (q, kv, table, table_width, positions, item_start, items, T, min_tokens, bias, sink, out, hq, hkv, dim, vdim,
-//  page_size, window, chunk, reach, scale, stream)
+//  page_size, window, chunk, reach, scale, keep_first, stream)
 PSB_API int psb_attention_biased_mma(const void* q, const void* kv, const void* table, int table_width, const void* positions,
                                      const void* item_start, int items, int T, int min_tokens, const void* bias, const void* sink,
                                      void* out, int hq, int hkv, int dim, int vdim, int page_size, int window, int chunk, int reach,
-                                     float scale, cudaStream_t stream) {
+                                     float scale, int keep_first, cudaStream_t stream) {
   if (!psb_attention_biased_mma_supported(hq, hkv, dim, vdim)) PSB_REFUSE("attention_biased_mma: shape not taken");
+  if (keep_first < 0 || (keep_first > 0 && (window < 1 || chunk > 0))) PSB_REFUSE("attention_biased_mma: kept first keys go with a window and no chunk mask");
   if (page_size < 1 || table_width < 1 || window < 0 || chunk < 0 || (bias && reach < 1)) PSB_REFUSE("attention_biased_mma: bad arguments");
   if ((((uintptr_t)q | (uintptr_t)kv) & 15) || hq > 65535) PSB_REFUSE("attention_biased_mma: operands must be 16-byte aligned");
   if (items < 1 || T < 1 || min_tokens < 1) return 0;
@@ -632,7 +670,7 @@ PSB_API int psb_attention_biased_mma(const void* q, const void* kv, const void* 
   psb_launch(attention_biased_mma_kernel<D_, V_>, grid, block, 0, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv,    \
              (const int32_t*)table, table_width, (const int32_t*)positions, (const int32_t*)item_start, items, min_tokens,     \
              (const float*)bias, (const float*)sink, (__nv_bfloat16*)out, hq, hkv, dim, vdim, page_size, window, chunk, reach, \
-             scale)
+             scale, keep_first)
   if (dim <= 64 && vdim <= 64) MMA_CASE(64, 64);
   else if (dim <= 64) MMA_CASE(64, 128);
   else if (vdim <= 64) MMA_CASE(128, 64);
@@ -655,11 +693,13 @@ PSB_API int psb_attention_biased_tile_supported(int hq, int hkv, int dim, int vd
 // The tiled kernel over every portion of at least ``min_tokens`` tokens (the grid is sized by an upper bound on their
 // tiles, so its shape depends on T and the number of items only).  Other tokens are left untouched.
 // (q, kv, table, table_width, positions, item_start, items, T, min_tokens, bias, sink, out, hq, hkv, dim, vdim,
-//  page_size, window, chunk, reach, scale, stream)
+//  page_size, window, chunk, reach, scale, keep_first, stream)
 PSB_API int psb_attention_biased_tiles(const void* q, const void* kv, const void* table, int table_width, const void* positions,
                                        const void* item_start, int items, int T, int min_tokens,
                                        const void* bias, const void* sink, void* out, int hq, int hkv, int dim, int vdim,
-                                       int page_size, int window, int chunk, int reach, float scale, cudaStream_t stream) {
+                                       int page_size, int window, int chunk, int reach, float scale, int keep_first,
+                                       cudaStream_t stream) {
+  if (keep_first < 0 || (keep_first > 0 && (window < 1 || chunk > 0))) PSB_REFUSE("attention_biased_tiles: kept first keys go with a window and no chunk mask");
   if (items < 1 || T < 1 || min_tokens < 1) return 0;
   const int tiles = (T + TILE_T - 1) / TILE_T + items;
   if (!psb_attention_biased_tile_supported(hq, hkv, dim, vdim)) PSB_REFUSE("attention_biased_tiles: shape not taken");
@@ -680,7 +720,7 @@ PSB_API int psb_attention_biased_tiles(const void* q, const void* kv, const void
     psb_launch(kernel, grid, block, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv, (const int32_t*)table,    \
                table_width, (const int32_t*)positions, (const int32_t*)item_start, items, min_tokens,                          \
                (const float*)bias, (const float*)sink, (__nv_bfloat16*)out, hq, hkv, dim, vdim,                                \
-               page_size, window, chunk, reach, scale);                                                                        \
+               page_size, window, chunk, reach, scale, keep_first);                                                            \
     launched = true;                                                                                                           \
   }
 #define TILE_ROW(DP_) TILE_CASE(DP_, 32) TILE_CASE(DP_, 64) TILE_CASE(DP_, 128) TILE_CASE(DP_, 256)

@@ -31,7 +31,7 @@ attention_prepare_kernel(const T* __restrict__ proj, long long ld, const int32_t
                          const float* __restrict__ cos_t, const float* __restrict__ sin_t, const float* __restrict__ head_factor,
                          TKV* __restrict__ kv, T* __restrict__ q_out, int hq, int hkv, int dim, int vdim, int page_size,
                          int num_pages, int max_positions, int rotary_dim, int interleaved, float eps, int values_are_keys,
-                         int split_planes) {
+                         int split_planes, const float* __restrict__ bias, int write_kv) {
   __shared__ float rows[PREP_WARPS][PREP_MAX_D];
   pdl_trigger();
   pdl_wait();
@@ -40,7 +40,7 @@ attention_prepare_kernel(const T* __restrict__ proj, long long ld, const int32_t
   const int qw = hq * dim, kw = hkv * dim;
   const T* row = proj + (size_t)t * ld;  // ld >= the row's width: the projection may be a run of columns of a wider product
   const int p = positions[t];
-  const int page = table[(size_t)token_item[t] * table_width + p / page_size];
+  const int page = write_kv ? table[(size_t)token_item[t] * table_width + p / page_size] : -1;
   const bool page_ok = page >= 0 && page < num_pages;  // tables are checked on the host; never write outside the pool
   const int rw = dim + vdim;
   const int half = rotary_dim / 2;
@@ -48,10 +48,12 @@ attention_prepare_kernel(const T* __restrict__ proj, long long ld, const int32_t
   const float* cs = turn ? cos_t + (size_t)p * half : nullptr;
   const float* sn = turn ? sin_t + (size_t)p * half : nullptr;
   float* mine = rows[warp];
-  for (int head = warp; head < hq + hkv; head += PREP_WARPS) {
+  // ``bias`` (float32, one number per column of the row, optional) is added to the projection in float32;
+  // ``write_kv`` 0: the row holds queries only (a layer that reads another layer's keys and values)
+  for (int head = warp; head < hq + (write_kv ? hkv : 0); head += PREP_WARPS) {
     const bool is_q = head < hq;
     const T* src = row + (size_t)head * dim;  // query heads, then key heads, lie one after the other
-    for (int d = lane; d < dim; d += 32) mine[d] = to_float<T>(src[d]);
+    for (int d = lane; d < dim; d += 32) mine[d] = to_float<T>(src[d]) + (bias ? bias[(size_t)head * dim + d] : 0.f);
     __syncwarp();
     if (turn) {
       for (int i = lane; i < half; i += 32) {
@@ -81,7 +83,8 @@ attention_prepare_kernel(const T* __restrict__ proj, long long ld, const int32_t
       TKV* vdst = split_planes ? dst + (size_t)hkv * page_size * dim : dst + dim;
       for (int d = lane; d < dim; d += 32) dst[d] = from_float<TKV>(mine[d] * factor);
       const T* vsrc = values_are_keys ? src : row + qw + kw + (size_t)g * vdim;
-      for (int d = lane; d < vdim; d += 32) vdst[d] = from_float<TKV>(to_float<T>(vsrc[d]));
+      const float* vb = bias ? (values_are_keys ? bias + (size_t)head * dim : bias + qw + kw + (size_t)g * vdim) : nullptr;
+      for (int d = lane; d < vdim; d += 32) vdst[d] = from_float<TKV>(to_float<T>(vsrc[d]) + (vb ? vb[d] : 0.f));
     }
     __syncwarp();
   }
@@ -202,15 +205,17 @@ attention_prepare_rows_kernel(const T* __restrict__ proj, long long ld, const in
              hq, hkv, page_size, num_pages, max_positions, rotary_dim, eps, values_are_keys, split_planes, groups)
 
 // (proj, ld, dtype, positions, token_item, table, table_width, cos, sin, head_factor, kv, kv_dtype, q_out, T, hq, hkv, dim, vdim,
-//  page_size, num_pages, max_positions, rotary_dim, interleaved, eps, values_are_keys, split_planes, stream)
+//  page_size, num_pages, max_positions, rotary_dim, interleaved, eps, values_are_keys, split_planes, bias, write_kv, stream)
 PSB_API int psb_attention_prepare(const void* proj, long long ld, int dtype, const void* positions, const void* token_item, const void* table,
                                   int table_width, const void* cos_t, const void* sin_t, const void* head_factor, void* kv,
                                   int kv_dtype, void* q_out, int T, int hq, int hkv, int dim, int vdim, int page_size,
                                   int num_pages, int max_positions, int rotary_dim, int interleaved, float eps,
-                                  int values_are_keys, int split_planes, cudaStream_t stream) {
-  if (T < 0 || hq < 1 || hkv < 1 || dim < 1 || dim > PREP_MAX_D || vdim < 1 || page_size < 1 || table_width < 1 || num_pages < 1)
+                                  int values_are_keys, int split_planes, const void* bias, int write_kv, cudaStream_t stream) {
+  if (T < 0 || hq < 1 || hkv < 1 || dim < 1 || dim > PREP_MAX_D || vdim < 1 || page_size < 1 || (write_kv && (table_width < 1 || num_pages < 1)))
     PSB_REFUSE("attention_prepare: bad sizes (heads %d/%d, sizes %d/%d, at most %d)", hq, hkv, dim, vdim, PREP_MAX_D);
-  if (ld < (long long)(hq + hkv) * dim + (values_are_keys ? 0 : (long long)hkv * vdim)) PSB_REFUSE("attention_prepare: row stride %lld is shorter than the row", ld);
+  if (write_kv && (!kv || !table)) PSB_REFUSE("attention_prepare: appending keys and values needs the cache entry and the page table");
+  if (ld < (long long)hq * dim + (write_kv ? (long long)hkv * dim + (values_are_keys ? 0 : (long long)hkv * vdim) : 0))
+    PSB_REFUSE("attention_prepare: row stride %lld is shorter than the row", ld);
   if (values_are_keys && vdim != dim) PSB_REFUSE("attention_prepare: keys that serve as values need vdim == dim, not %d and %d", vdim, dim);
   if ((cos_t == nullptr) != (sin_t == nullptr)) PSB_REFUSE("attention_prepare: cosines and sines come together");
   if (cos_t && (rotary_dim < 2 || rotary_dim % 2 || rotary_dim > dim || max_positions < 1))
@@ -218,7 +223,7 @@ PSB_API int psb_attention_prepare(const void* proj, long long ld, int dtype, con
   if (split_planes && vdim != dim) PSB_REFUSE("attention_prepare: keys and values in planes of their own need vdim == dim, not %d and %d", vdim, dim);
   if (T == 0) return 0;
   // heads in registers: sizes that give every lane an even run, a rotation (if any) of neighbours, rows that allow wide loads
-  const bool rows_fit = vdim == dim && (dim == 64 || dim == 128 || dim == 256) && (cos_t == nullptr || interleaved);
+  const bool rows_fit = vdim == dim && (dim == 64 || dim == 128 || dim == 256) && (cos_t == nullptr || interleaved) && !bias && write_kv;
   if (rows_fit) {
     // long steps: four heads a warp, their loads in flight together; short ones: a head a warp, as many warps as there are heads
     const int hpw = (long long)T * (hq + hkv) >= 4096 ? 4 : 1;
@@ -254,7 +259,7 @@ PSB_API int psb_attention_prepare(const void* proj, long long ld, int dtype, con
       psb_launch(attention_prepare_kernel<T_, TKV>, dim3(T), dim3(PREP_WARPS * 32), 0, stream, (const T_*)proj, ld,
                  (const int32_t*)positions, (const int32_t*)token_item, (const int32_t*)table, table_width, (const float*)cos_t,
                  (const float*)sin_t, (const float*)head_factor, (TKV*)kv, (T_*)q_out, hq, hkv, dim, vdim, page_size, num_pages,
-                 max_positions, rotary_dim, interleaved, eps, values_are_keys, split_planes);
+                 max_positions, rotary_dim, interleaved, eps, values_are_keys, split_planes, (const float*)bias, write_kv);
     });
   });
   PSB_LAUNCH_CHECK("attention_prepare");

@@ -60,9 +60,19 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 // x[i] = gain * ((h[r] + delta[r]) * rsqrt(mean((h[r]+delta[r])^2) + eps));  r = rows ? rows[i] : i.
 // With update_h the sum is stored back into h[r] (float32 residual stream).
+// ``dscale`` / ``dshift`` (float32 [H], each optional): the sublayer's output joins the stream as
+// (delta + dshift) * dscale, channel by channel (an output bias that was left out of the product; a learned scale
+// per channel on the sublayer's result), in float32.
+__device__ __forceinline__ float affine_delta(float d, const float* __restrict__ dscale, const float* __restrict__ dshift, int j) {
+  if (dshift) d += dshift[j];
+  if (dscale) d *= dscale[j];
+  return d;
+}
+
 template <typename TD, typename TX>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ gain,
-                                   const int32_t* __restrict__ rows, TX* __restrict__ x, int H, float eps, int update_h) {
+                                   const int32_t* __restrict__ rows, TX* __restrict__ x, int H, float eps, int update_h,
+                                   const float* __restrict__ dscale, const float* __restrict__ dshift) {
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();
@@ -73,7 +83,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
   float ss = 0.f;
   for (int j = threadIdx.x; j < H; j += blockDim.x) {
     float v = hr[j];
-    if (dr) v += to_float<TD>(dr[j]);
+    if (dr) v += affine_delta(to_float<TD>(dr[j]), dscale, dshift, j);
     ss += v * v;
   }
   const float total = block_sum(ss, scratch);
@@ -81,7 +91,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
   TX* xr = x + (size_t)i * H;
   for (int j = threadIdx.x; j < H; j += blockDim.x) {
     float v = hr[j];
-    if (dr) v += to_float<TD>(dr[j]);
+    if (dr) v += affine_delta(to_float<TD>(dr[j]), dscale, dshift, j);
     if (update_h && dr) hr[j] = v;
     xr[j] = from_float<TX>(gain[j] * (v * inv));
   }
@@ -160,7 +170,8 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const fl
 // Residual add + RMSNorm with the row held in registers: one pass over memory.  H % 8 == 0, H <= 8 * VPT * blockDim.
 template <typename TD, typename TX, int VPT>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ gain,
-                                       const int32_t* __restrict__ rows, TX* __restrict__ x, int H, float eps, int update_h) {
+                                       const int32_t* __restrict__ rows, TX* __restrict__ x, int H, float eps, int update_h,
+                                       const float* __restrict__ dscale, const float* __restrict__ dshift) {
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();
@@ -178,6 +189,18 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
       if (dr) {
         float d[8];
         load8<TD>(dr + j, d);
+        if (dshift) {
+          float b[8];
+          load8<float>(dshift + j, b);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) d[k] += b[k];
+        }
+        if (dscale) {
+          float g[8];
+          load8<float>(dscale + j, g);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) d[k] *= g[k];
+        }
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[c][k] += d[k];
       }
@@ -216,8 +239,11 @@ PSB_API int psb_embedding(const void* ids, const void* table, int table_dtype, v
   return 0;
 }
 
+// (h, delta, delta_dtype, gain, rows, x, x_dtype, n_rows, H, eps, update_h, delta_scale, delta_shift, stream)
 PSB_API int psb_add_rmsnorm(void* h, const void* delta, int delta_dtype, const void* gain, const void* rows, void* x,
-                            int x_dtype, int n_rows, int H, float eps, int update_h, cudaStream_t stream) {
+                            int x_dtype, int n_rows, int H, float eps, int update_h, const void* dscale, const void* dshift,
+                            cudaStream_t stream) {
+  if ((dscale || dshift) && !delta) PSB_REFUSE("add_rmsnorm: a scale or shift needs a sublayer output to apply to");
   if (n_rows < 0 || H < 1) PSB_REFUSE("add_rmsnorm: bad sizes rows=%d H=%d", n_rows, H);
   if (!(eps > 0.f)) PSB_REFUSE("add_rmsnorm: eps must be positive");
   if (n_rows == 0) return 0;
@@ -228,7 +254,7 @@ PSB_API int psb_add_rmsnorm(void* h, const void* delta, int delta_dtype, const v
       PSB_DISPATCH_DTYPE(x_dtype, TX, {
         auto launch = [&](auto kernel) {
           psb_launch(kernel, dim3(n_rows), dim3(threads), 0, stream, (float*)h, (const TD*)delta, (const float*)gain,
-                     (const int32_t*)rows, (TX*)x, H, eps, update_h);
+                     (const int32_t*)rows, (TX*)x, H, eps, update_h, (const float*)dscale, (const float*)dshift);
         };
         if (vpt == 1) launch(add_rmsnorm_vec_kernel<TD, TX, 1>);
         else if (vpt == 2) launch(add_rmsnorm_vec_kernel<TD, TX, 2>);
@@ -243,7 +269,8 @@ PSB_API int psb_add_rmsnorm(void* h, const void* delta, int delta_dtype, const v
   PSB_DISPATCH_DTYPE(delta_dtype, TD, {
     PSB_DISPATCH_DTYPE(x_dtype, TX, {
       psb_launch(add_rmsnorm_kernel<TD, TX>, dim3(n_rows), dim3(threads), 0, stream, (float*)h, (const TD*)delta, (const float*)gain,
-                                                                 (const int32_t*)rows, (TX*)x, H, eps, update_h);
+                                                                 (const int32_t*)rows, (TX*)x, H, eps, update_h,
+                                                                 (const float*)dscale, (const float*)dshift);
     });
   });
   PSB_LAUNCH_CHECK("add_rmsnorm");

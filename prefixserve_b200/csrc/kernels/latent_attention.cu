@@ -59,7 +59,7 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, const int32_t*
     const float v = to_float<T>(row[j]);
     ss += v * v;
   }
-  const float inv_q = 1.f / sqrtf(block_total(ss, scratch) / (float)q_rank + eps);
+  const float inv_q = q_rank > 0 ? 1.f / sqrtf(block_total(ss, scratch) / (float)q_rank + eps) : 0.f;  // q_rank 0: no query latent in the row
   for (int j = threadIdx.x; j < q_rank; j += blockDim.x)
     cq_out[(size_t)t * q_rank + j] = from_float<T>(gain_q[j] * (to_float<T>(row[j]) * inv_q));
 
@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 latent_attention_kernel(const float* __restrict__ q_lat, const TKV* __restrict__ cache, const int32_t* __restrict__ table,
                         int table_width, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_item,
                         const float* __restrict__ gate, TO* __restrict__ out, int T_tokens, int heads, int rank, int rot,
-                        int page_size, int num_pages, int window, float scale) {
+                        int page_size, int num_pages, int window, float scale, const float* __restrict__ sink) {
   extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   pdl_wait();
@@ -249,10 +249,11 @@ latent_attention_kernel(const float* __restrict__ q_lat, const TKV* __restrict__
     if (d + 1 < rank) part_o[(size_t)warp * rank + d + 1] = acc[i][1];
   }
   __syncthreads();
-  float m_all = -FLT_MAX;
+  // ``sink`` (a score per head, optional): one more term of the denominator, without a key or a value
+  float m_all = sink ? sink[h] : -FLT_MAX;
 #pragma unroll
   for (int w = 0; w < WARPS; ++w) m_all = fmaxf(m_all, part_ml[2 * w]);
-  float f[WARPS], l_all = 0.f;
+  float f[WARPS], l_all = sink ? expf(sink[h] - m_all) : 0.f;
 #pragma unroll
   for (int w = 0; w < WARPS; ++w) {
     f[w] = part_ml[2 * w + 1] > 0.f ? expf(part_ml[2 * w] - m_all) : 0.f;
@@ -283,7 +284,7 @@ latent_attention_rows_kernel(const float* __restrict__ q_lat, const __nv_bfloat1
                              const int32_t* __restrict__ table, int table_width, const int32_t* __restrict__ positions,
                              const int32_t* __restrict__ token_item, const float* __restrict__ gate, TO* __restrict__ out,
                              float* __restrict__ partial, int heads, int rank, int rot, int page_size, int num_pages,
-                             int window, float scale) {
+                             int window, float scale, const float* __restrict__ sink) {
   extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   pdl_wait();
@@ -441,6 +442,13 @@ latent_attention_rows_kernel(const float* __restrict__ q_lat, const __nv_bfloat1
       }
       continue;
     }
+    if (sink) {  // the sink joins the denominator where a (token, head)'s keys are whole (else in the merge kernel)
+      const float sk = sink[h0 + hh], top = fmaxf(m_all, sk);
+      const float down = expf(m_all - top);
+      l_all = l_all * down + expf(sk - top);
+#pragma unroll
+      for (int w = 0; w < ROW_WARPS; ++w) f[w] *= down;
+    }
     const float wgt = (gate ? gate[(size_t)t * heads + h0 + hh] : 1.f) / l_all;
     TO* orow = out + ((size_t)t * heads + h0 + hh) * rank;
     for (int d = threadIdx.x; d < rank; d += blockDim.x) {
@@ -457,14 +465,16 @@ constexpr int MAX_SPLITS = 8;
 
 template <typename TO>
 __global__ void latent_attention_merge_kernel(const float* __restrict__ partial, const float* __restrict__ gate,
-                                              TO* __restrict__ out, int rank, int splits) {
+                                              TO* __restrict__ out, int rank, int splits, const float* __restrict__ sink,
+                                              int heads) {
   pdl_trigger();
   pdl_wait();
   const size_t unit = blockIdx.x;  // token * heads + head
   const float* mine = partial + unit * splits * (rank + 2);
-  float m_all = -FLT_MAX;
+  const float sk = sink ? sink[unit % heads] : -FLT_MAX;
+  float m_all = sk;
   for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, mine[(size_t)s * (rank + 2)]);
-  float f[MAX_SPLITS], l_all = 0.f;
+  float f[MAX_SPLITS], l_all = sink ? expf(sk - m_all) : 0.f;
 #pragma unroll
   for (int s = 0; s < MAX_SPLITS; ++s) {
     f[s] = 0.f;
@@ -636,7 +646,7 @@ PSB_API int psb_latent_prepare(const void* proj, int dtype, const void* position
                                const void* gain_kv, void* cq_out, void* gate_out, void* cache, int cache_dtype, int T,
                                int q_rank, int rank, int rot, int rot_dims, int heads, int page_size, int num_pages,
                                int max_positions, float eps, cudaStream_t stream) {
-  if (T < 0 || q_rank < 1 || rank < 1 || rot < 0 || heads < 0) PSB_REFUSE("latent_prepare: bad sizes T=%d q_rank=%d rank=%d rot=%d heads=%d", T, q_rank, rank, rot, heads);
+  if (T < 0 || q_rank < 0 || rank < 1 || rot < 0 || heads < 0) PSB_REFUSE("latent_prepare: bad sizes T=%d q_rank=%d rank=%d rot=%d heads=%d", T, q_rank, rank, rot, heads);
   if (rot_dims < 0 || rot_dims > rot || rot_dims % 2) PSB_REFUSE("latent_prepare: %d rotated dimensions must be even and within the rotated part of %d", rot_dims, rot);
   if (rot_dims > 0 && (!cos_t || !sin_t || max_positions < 1)) PSB_REFUSE("latent_prepare: angle tables missing");
   if (page_size < 1 || num_pages < 1 || table_width < 1) PSB_REFUSE("latent_prepare: bad paging (page_size=%d pages=%d width=%d)", page_size, num_pages, table_width);
@@ -681,7 +691,7 @@ PSB_API int psb_latent_attention_rows_supported(int cache_dtype, int rank, int r
 PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache_dtype, const void* table, int table_width,
                                  const void* positions, const void* token_item, const void* gate, void* out, int out_dtype,
                                  int T, int heads, int rank, int rot, int page_size, int num_pages, int window, float scale,
-                                 int heads_per_block, int splits, void* partial, cudaStream_t stream) {
+                                 int heads_per_block, int splits, void* partial, const void* sink, cudaStream_t stream) {
   if (T < 0 || heads < 1 || rank < 1 || rot < 0) PSB_REFUSE("latent_attention: bad sizes T=%d heads=%d rank=%d rot=%d", T, heads, rank, rot);
   if (rank > 1024 || rank + rot > 2048) PSB_REFUSE("latent_attention: a latent of %d (+%d rotated) is beyond this kernel (1024, 2048 together)", rank, rot);
   if (page_size < 1 || num_pages < 1 || table_width < 1) PSB_REFUSE("latent_attention: bad paging (page_size=%d pages=%d width=%d)", page_size, num_pages, table_width);
@@ -711,7 +721,7 @@ PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache
         psb_launch(latent_attention_rows_kernel<TO, NP, HP>, dim3((unsigned)row_blocks, splits), dim3(ROW_WARPS * 32),   \
                    bytes, stream, (const float*)q_lat, (const __nv_bfloat16*)cache, (const int32_t*)table, table_width,  \
                    (const int32_t*)positions, (const int32_t*)token_item, (const float*)gate, (TO*)out, (float*)partial, \
-                   heads, rank, rot, page_size, num_pages, window, scale);                                               \
+                   heads, rank, rot, page_size, num_pages, window, scale, (const float*)sink);                           \
       });                                                                                                                \
     } while (0)
     if (hp == 2) {
@@ -724,7 +734,7 @@ PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache
     if (splits > 1) {
       PSB_DISPATCH_DTYPE(out_dtype, TO, {
         psb_launch(latent_attention_merge_kernel<TO>, dim3((unsigned)blocks), dim3(128), 0, stream, (const float*)partial,
-                   (const float*)gate, (TO*)out, rank, splits);
+                   (const float*)gate, (TO*)out, rank, splits, (const float*)sink, heads);
       });
       PSB_LAUNCH_CHECK("latent_attention_merge");
     }
@@ -737,7 +747,7 @@ PSB_API int psb_latent_attention(const void* q_lat, const void* cache, int cache
       psb_launch(latent_attention_kernel<TKV, TO, NACC>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream,        \
                  (const float*)q_lat, (const TKV*)cache, (const int32_t*)table, table_width, (const int32_t*)positions,  \
                  (const int32_t*)token_item, (const float*)gate, (TO*)out, T, heads, rank, rot, page_size, num_pages,    \
-                 window, scale);                                                                                         \
+                 window, scale, (const float*)sink);                                                                     \
     });                                                                                                                  \
   })
   if (rank <= 128) { LATENT_LAUNCH(2); }        // NACC pairs of columns a lane: 64 columns each

@@ -1,11 +1,12 @@
 // A routed feed-forward (mixture of experts): router, grouping of the chosen (token, expert) pairs by expert, the two
 // products of every expert over its own rows, and the weighted sum.
 //
-// moe_route_kernel (a warp per token): scores s = sigmoid(z) of the float32 router logits z [T, E(+1)]; the choice is
-// made on s + correction, the weights on s.  With ``groups`` > 1 the experts form that many equal groups of
-// neighbours; a group's score is the sum of its two largest choice scores and only the experts of the ``keep`` best
-// groups can be chosen.  The ``top`` largest choice scores win (the lower index on a tie); their weights are
-// s / (sum of the chosen s + 1e-20) * scale.
+// moe_route_kernel (a warp per token): scores s of the float32 router logits z [T, E(+1)]: sigmoid(z), or
+// (``softmax_scores``) the softmax of z over all experts; the choice is made on s + correction, the weights on s.
+// With ``groups`` > 1 the experts form that many equal groups of neighbours; a group's score is the sum of its two
+// largest choice scores, or (``group_by_max``) its largest, and only the experts of the ``keep`` best groups can be
+// chosen.  The ``top`` largest choice scores win (the lower index on a tie); their weights are
+// s / (sum of the chosen s + 1e-20) * scale, or (``normalize`` 0) s * scale as it is.
 //
 // moe_group_kernel (one block): counts the pairs of every expert, lays the experts' rows out one after the other
 // (offsets [E + 1]; every expert's first row a multiple of ``pad``, the rows in between belong to nobody) and gives
@@ -41,7 +42,8 @@ constexpr int ROUTE_WARPS = 4;
 
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ correction, int32_t* __restrict__ chosen,
-                 float* __restrict__ weight, int T, int E, int top, int groups, int keep, float scale) {
+                 float* __restrict__ weight, int T, int E, int top, int groups, int keep, float scale, int softmax_scores,
+                 int group_by_max, int normalize) {
   extern __shared__ float sm[];  // per warp: s[E], choice[E], group score[groups]
   pdl_trigger();
   pdl_wait();
@@ -51,8 +53,16 @@ moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__
   float* s = sm + (size_t)warp * (2 * E + groups);
   float* choice = s + E;
   float* gscore = choice + E;
+  float z_top = -FLT_MAX, z_sum = 1.f;
+  if (softmax_scores) {
+    for (int e = lane; e < E; e += 32) z_top = fmaxf(z_top, z[(size_t)t * ldz + e]);
+    z_top = warp_max(z_top);
+    float part = 0.f;
+    for (int e = lane; e < E; e += 32) part += expf(z[(size_t)t * ldz + e] - z_top);
+    z_sum = warp_sum(part);
+  }
   for (int e = lane; e < E; e += 32) {
-    const float v = sigmoidf_(z[(size_t)t * ldz + e]);
+    const float v = softmax_scores ? expf(z[(size_t)t * ldz + e] - z_top) / z_sum : sigmoidf_(z[(size_t)t * ldz + e]);
     s[e] = v;
     choice[e] = v + (correction ? correction[e] : 0.f);
   }
@@ -66,7 +76,7 @@ moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__
         if (c > a) { b = a; a = c; }
         else if (c > b) b = c;
       }
-      gscore[g] = per > 1 ? a + b : a;
+      gscore[g] = (per > 1 && !group_by_max) ? a + b : a;
     }
     __syncwarp();
     // a group is dropped when at least ``keep`` groups come before it (larger score, or equal and a lower index)
@@ -106,7 +116,7 @@ moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__
   }
   if (lane < top) {
     chosen[(size_t)t * top + lane] = mine_e;
-    weight[(size_t)t * top + lane] = mine_s / (total + 1e-20f) * scale;
+    weight[(size_t)t * top + lane] = (normalize ? mine_s / (total + 1e-20f) : mine_s) * scale;
   }
 }
 
@@ -438,16 +448,18 @@ __global__ void moe_combine_kernel(const TY* __restrict__ Y, const int32_t* __re
 
 }  // namespace
 
-// (z, ldz, correction, chosen, weight, T, E, top, groups, keep, scale, stream)
+// (z, ldz, correction, chosen, weight, T, E, top, groups, keep, scale, softmax_scores, group_by_max, normalize, stream)
 PSB_API int psb_moe_route(const void* z, int ldz, const void* correction, void* chosen, void* weight, int T, int E, int top,
-                          int groups, int keep, float scale, cudaStream_t stream) {
+                          int groups, int keep, float scale, int softmax_scores, int group_by_max, int normalize,
+                          cudaStream_t stream) {
   if (T < 0 || E < 1 || E > MAX_EXPERTS || top < 1 || top > MAX_TOP || top > E || ldz < E) PSB_REFUSE("moe_route: bad sizes E=%d top=%d", E, top);
   if (groups < 1 || E % groups || keep < 1 || keep > groups) PSB_REFUSE("moe_route: %d experts cannot form %d groups of which %d are kept", E, groups, keep);
   if ((E / groups) * keep < top) PSB_REFUSE("moe_route: %d kept groups of %d experts cannot give %d choices", keep, E / groups, top);
   if (T == 0) return 0;
   const size_t smem = sizeof(float) * ROUTE_WARPS * (2 * (size_t)E + groups);
   psb_launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream, (const float*)z, ldz,
-             (const float*)correction, (int32_t*)chosen, (float*)weight, T, E, top, groups, keep, scale);
+             (const float*)correction, (int32_t*)chosen, (float*)weight, T, E, top, groups, keep, scale, softmax_scores,
+             group_by_max, normalize);
   PSB_LAUNCH_CHECK("moe_route");
   return 0;
 }

@@ -401,7 +401,8 @@ class Scheduler:
         def most_pages(g) -> int:
             whole = pages_for(total, page)
             reach = min((x for x in (g.window, g.chunk) if x is not None), default=None)
-            return whole if reach is None else min(whole, pages_for(reach + self._chunk, page) + 1)
+            kept = pages_for(g.keep_first, page) if getattr(g, "keep_first", 0) else 0
+            return whole if reach is None else min(whole, pages_for(reach + self._chunk, page) + 1 + kept)
 
         checks = (
             (req_id in self._by_id, AddResult.DUPLICATE_ID),

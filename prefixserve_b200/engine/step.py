@@ -209,6 +209,9 @@ class ModelRunner:
                 low = np.maximum(low, starts // g.chunk * g.chunk)
             first = (low // page).astype(np.int32)
             bad = cache.covered(gi, slots, first, upto)
+            if bad < 0 and g.keep_first:  # the pages of the kept first keys, as far as the sequence has got
+                kept = np.minimum(pages_for(g.keep_first, page), upto).astype(np.int32)
+                bad = cache.covered(gi, slots, np.zeros(len(slots), dtype=np.int32), kept)
             if bad >= 0:
                 raise EngineError(f"slot {int(slots[bad])}: page table of group {gi} lacks a page or names one outside the pool")
         if self.check_writes and cache.tree is not None:

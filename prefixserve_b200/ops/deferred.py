@@ -41,6 +41,25 @@ class PostNormed:
         self.shape, self.dtype = tuple(y.shape), y.dtype
 
 
+class Affine:
+    """A sublayer's result that joins the stream as (y + shift) * scale, channel by channel: ``shift`` is a bias of the
+    sublayer's last product that was left out of it, ``scale`` a learned factor per channel on the sublayer's result
+    (each a float32 vector, or None).  It travels as the pending output of a block; the norm that meets it next does
+    the arithmetic in float32 inside its own kernel (``ops.add_rmsnorm``)."""
+
+    def __init__(self, y, scale: torch.Tensor | None = None, shift: torch.Tensor | None = None):
+        if isinstance(y, Affine):  # a scale around a result that already carries a shift (or a scale)
+            if shift is not None:
+                raise ValueError("a shift cannot be put around a result that is already scaled or shifted")
+            shift = y.shift
+            scale = scale if y.scale is None else (y.scale if scale is None else y.scale * scale)
+            y = y.y
+        if isinstance(y, PendingProduct):
+            y = y.tensor()
+        self.y, self.scale, self.shift = y, scale, shift
+        self.shape, self.dtype = tuple(y.shape), y.dtype
+
+
 class NormedRows:
     def __init__(self, h: torch.Tensor, pending, gain: torch.Tensor, eps: float,
                  dtype: torch.dtype, rows: torch.Tensor | None = None):
@@ -62,7 +81,7 @@ class NormedRows:
 
     @property
     def fusable(self) -> bool:
-        return self._x is None and not self._settled and not isinstance(self.pending, PendingProduct)
+        return self._x is None and not self._settled and not isinstance(self.pending, (PendingProduct, Affine))
 
     def raw(self):
         """(v * gain as bfloat16 [M, K], the tiles' shares of every row's sum(v^2) float32 [parts, 64]) with v = h + pending,

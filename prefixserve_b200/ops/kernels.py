@@ -10,7 +10,7 @@ import math
 
 import torch
 
-from .deferred import NormedRows, PendingProduct, PostNormed
+from .deferred import Affine, NormedRows, PendingProduct, PostNormed
 from .library import KernelError, check, lib, stream_handle
 
 F32, BF16 = 0, 1
@@ -65,6 +65,9 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None =
 def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, gain: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
     """h += delta (float32, in place, unless ``rows``); returns gain * rmsnorm(h) for all or the chosen rows."""
+    dscale = dshift = None
+    if isinstance(delta, Affine):  # joins the stream as (y + shift) * scale
+        delta, dscale, dshift = delta.y, delta.scale, delta.shift
     if isinstance(delta, PendingProduct):
         delta = delta.tensor()
     _dev(h, "residual stream")
@@ -80,13 +83,17 @@ def add_rmsnorm(h: torch.Tensor, delta: torch.Tensor | None, gain: torch.Tensor,
         if delta.shape != h.shape:
             raise KernelError(f"sublayer output {tuple(delta.shape)} does not match the stream {tuple(h.shape)}")
         dcode = _code(delta, "sublayer output")
+        for what, v in (("scale", dscale), ("shift", dshift)):
+            if v is not None:
+                _f32_vector(v, width, f"the sublayer output's {what}")
     n = h.shape[0]
     if rows is not None:
         _i32(rows, "row index")
         n = rows.numel()
     x = torch.empty((n, width), dtype=out_dtype, device=h.device)
     check(lib().psb_add_rmsnorm(h.data_ptr(), _ptr(delta), dcode, gain.data_ptr(), _ptr(rows), x.data_ptr(),
-                                _code(x, "norm output"), n, width, float(eps), 0 if rows is not None else 1, _stream()),
+                                _code(x, "norm output"), n, width, float(eps), 0 if rows is not None else 1, _ptr(dscale),
+                                _ptr(dshift), _stream()),
           "add_rmsnorm")
     return x
 
@@ -543,6 +550,8 @@ def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, token_item: torc
     if cache.numel() % (page_size * (rank + rot)) or cache.shape[-1] != rank + rot or cache.shape[-2] != page_size:
         raise KernelError(f"cache entry must be [pages, .., {page_size}, {rank + rot}], is {tuple(cache.shape)}")
     for what, g, n in (("query latent gain", gain_q, q_rank), ("key/value latent gain", gain_kv, rank)):
+        if n == 0 and g is None:  # no query latent in the row (queries projected directly)
+            continue
         if g.dtype != torch.float32 or g.numel() != n or not g.is_cuda:
             raise KernelError(f"{what} must be float32 [{n}] on the device")
     max_pos = 0
@@ -554,7 +563,7 @@ def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, token_item: torc
     cq = torch.empty((t, q_rank), dtype=proj.dtype, device=proj.device)
     gate = torch.empty((t, heads), dtype=torch.float32, device=proj.device)
     check(lib().psb_latent_prepare(proj.data_ptr(), _code(proj, "projection output"), positions.data_ptr(), token_item.data_ptr(),
-                                   table.data_ptr(), table.shape[1], _ptr(cos), _ptr(sin), gain_q.data_ptr(), gain_kv.data_ptr(),
+                                   table.data_ptr(), table.shape[1], _ptr(cos), _ptr(sin), _ptr(gain_q), gain_kv.data_ptr(),
                                    cq.data_ptr(), gate.data_ptr(), cache.data_ptr(), _code(cache, "cache entry"), t, q_rank, rank,
                                    rot, rot_dims, heads, page_size, cache.shape[0], max_pos, float(eps), _stream()), "latent_prepare")
     return cq, gate
@@ -573,6 +582,17 @@ def latent_query_rotate(q: torch.Tensor, positions: torch.Tensor, cos: torch.Ten
           "latent_query_rotate")
 
 
+def gate_mul(x: torch.Tensor, gate: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """x * gate element by element (gate float32, e.g. a sigmoid already taken; the product in float32), in ``out_dtype``."""
+    _dev(x, "gated values"), _dev(gate, "gate")
+    if gate.dtype != torch.float32 or gate.numel() != x.numel():
+        raise KernelError(f"the gate must be float32 with {x.numel()} numbers, is {gate.dtype} {tuple(gate.shape)}")
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    check(lib().psb_gate_mul(x.data_ptr(), _code(x, "gated values"), gate.data_ptr(), out.data_ptr(), _code(out, "gated output"),
+                             x.numel(), _stream()), "gate_mul")
+    return out
+
+
 BAND_MIN_TOKENS = 64    # portions from this many tokens on take the banded form of latent attention (bfloat16, with a window)
 BAND_CHUNK = 256        # tokens of a portion whose band of keys is handled by one set of products
 BAND_MAX_WINDOW = 8192  # wider windows stay with the kernel that walks the keys
@@ -580,14 +600,18 @@ BAND_MAX_WINDOW = 8192  # wider windows stay with the kernel that walks the keys
 
 def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
                      token_item: torch.Tensor, gate: torch.Tensor | None, *, rank: int, page_size: int, window: int | None,
-                     scale: float, out_dtype: torch.dtype, items=None, key_hint: int = 0) -> torch.Tensor:
+                     scale: float, out_dtype: torch.dtype, items=None, key_hint: int = 0,
+                     sink: torch.Tensor | None = None) -> torch.Tensor:
     """Softmax attention of latent-space queries [T, heads, rank + rot] (float32) over the cached rows
     [pages, page_size, rank + rot]; returns sum_j p_j c_j times the head's gate, [T, heads, rank].
 
     ``items`` (the step's host-side item list): portions of ``BAND_MIN_TOKENS`` tokens or more of a bfloat16 cache with
     a window go through the banded form (the keys a run of tokens can see gathered into a matrix, scores and weighted
     sums as products on the tensor cores, softmax in float32 between them); single tokens and short portions through
-    the kernel that walks the keys.  Which form a token takes depends on its portion's length only."""
+    the kernel that walks the keys.  Which form a token takes depends on its portion's length only.
+
+    ``sink`` (float32 [heads]): a score per head whose exponential joins the softmax denominator once, without a key or
+    a value (every token then walks its keys: the banded form has no sink)."""
     _dev(q_lat, "latent queries"), _dev(cache, "cache entry")
     _i32(table, "page table"), _i32(positions, "positions"), _i32(token_item, "token-to-item map")
     t, heads, d = q_lat.shape
@@ -595,9 +619,11 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tens
         raise KernelError(f"latent queries {q_lat.dtype} {tuple(q_lat.shape)} do not fit the cache entry {tuple(cache.shape)}")
     if gate is not None and (gate.dtype != torch.float32 or tuple(gate.shape) != (t, heads) or not gate.is_cuda):
         raise KernelError(f"head gates must be float32 [{t}, {heads}]")
+    if sink is not None:
+        _f32_vector(sink, heads, "sinks")
     out = torch.empty((t, heads, rank), dtype=out_dtype, device=q_lat.device)
     banded = []
-    if (items is not None and window and window <= BAND_MAX_WINDOW and cache.dtype == torch.bfloat16 and d % 8 == 0
+    if (items is not None and sink is None and window and window <= BAND_MAX_WINDOW and cache.dtype == torch.bfloat16 and d % 8 == 0
             and rank % 8 == 0):
         banded = [(it.first_token, it.end - it.start) for it in items if it.end - it.start >= BAND_MIN_TOKENS]
     at = 0
@@ -605,7 +631,7 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tens
         if first > at:
             _latent_attention_walk(q_lat[at:first], cache, table, positions[at:first], token_item[at:first],
                                    None if gate is None else gate[at:first], out[at:first], rank, page_size, window, scale,
-                                   key_hint=int(window or key_hint))
+                                   key_hint=int(window or key_hint), sink=sink)
         at = first + n
     if banded:
         q16 = torch.empty((t, heads, d), dtype=torch.bfloat16, device=q_lat.device)
@@ -624,7 +650,7 @@ ROWS_KEYS_PER_SPLIT = 128  # no block of that kernel is given fewer keys than th
 
 
 def _latent_attention_walk(q_lat, cache, table, positions, token_item, gate, out, rank, page_size, window, scale,
-                           key_hint: int = 0) -> None:
+                           key_hint: int = 0, sink=None) -> None:
     """Tokens that walk their keys.  ``key_hint``: about how many keys the longest walk has (the window, or the step's
     longest sequence), for the choice of how many blocks share a (token, head)."""
     t, heads, d = q_lat.shape
@@ -640,7 +666,7 @@ def _latent_attention_walk(q_lat, cache, table, positions, token_item, gate, out
     check(lib().psb_latent_attention(q_lat.data_ptr(), cache.data_ptr(), _code(cache, "cache entry"), table.data_ptr(), table.shape[1],
                                      positions.data_ptr(), token_item.data_ptr(), _ptr(gate), out.data_ptr(), _code(out, "output"),
                                      t, heads, rank, d - rank, page_size, cache.shape[0], int(window or 0), float(scale), hp, splits,
-                                     _ptr(partial), _stream()),
+                                     _ptr(partial), _ptr(sink), _stream()),
           "latent_attention")
 
 
@@ -789,11 +815,15 @@ def biased_attention(qkv: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, c
 
 def attention_over_rows(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,
                         dim: int, vdim: int, page_size: int, scale: float, window: int | None = None, chunk: int | None = None,
-                        bias: torch.Tensor | None = None, sink: torch.Tensor | None = None) -> torch.Tensor:
+                        bias: torch.Tensor | None = None, sink: torch.Tensor | None = None, keep_first: int = 0) -> torch.Tensor:
     """Causal attention of queries [T, hq, dim] over a cache entry that holds one row per token and key/value head, the
     key and then the value ([pages, 1, hkv, page_size, dim + vdim]; the step's own rows already appended), with an
     optional window, chunk mask, distance bias (float32 [heads, reach]) and sink (float32 [heads]: a score per head
-    that joins the softmax denominator without a value) -> [T, hq * vdim]."""
+    that joins the softmax denominator without a value) -> [T, hq * vdim].  ``keep_first`` (with a window): the first so
+    many keys of a sequence stay visible to every later query."""
+    keep_first = int(keep_first or 0)
+    if keep_first and (not window or chunk):
+        raise KernelError("kept first keys go with a window and no chunk mask")
     _dev(q, "queries"), _dev(kv, "cache entry"), _i32(table, "page table")
     positions, token_item = _i32(ctx.positions, "positions"), _i32(ctx.token_item, "token-to-item map")
     t = q.shape[0]
@@ -824,12 +854,12 @@ def attention_over_rows(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, 
                                          table.data_ptr(), table.shape[1], positions.data_ptr(), token_item.data_ptr(),
                                          _ptr(bias), _ptr(sink), out.data_ptr(), t, num_heads, num_kv_heads, dim, vdim,
                                          page_size, win, chk, reach, float(scale), item_start.data_ptr(),
-                                         least if tiled else 0, _stream()), "attention_biased")
+                                         least if tiled else 0, keep_first, _stream()), "attention_biased")
     if tiled:
         entry = lib().psb_attention_biased_mma if on_tensor_cores else lib().psb_attention_biased_tiles
         check(entry(q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], positions.data_ptr(), item_start.data_ptr(),
                     ctx.num_items, t, least, _ptr(bias), _ptr(sink), out.data_ptr(), num_heads, num_kv_heads, dim,
-                    vdim, page_size, win, chk, reach, float(scale), _stream()),
+                    vdim, page_size, win, chk, reach, float(scale), keep_first, _stream()),
               "attention_biased_mma" if on_tensor_cores else "attention_biased_tiles")
     return out
 
@@ -877,10 +907,14 @@ def delta_rule(proj: torch.Tensor, ba: torch.Tensor, taps: torch.Tensor, a_log: 
 
 
 def moe_route(z: torch.Tensor, correction: torch.Tensor | None, *, experts: int, top: int, groups: int, keep: int,
-              scale: float):
+              scale: float, scores: str = "sigmoid", group_score: str = "top2", normalize: bool = True):
     """Router logits float32 [T, >= experts] (further columns are ignored) -> (chosen int32 [T, top], weights float32
-    [T, top]): sigmoid scores, choice by score + correction among the experts of the ``keep`` best of ``groups`` groups,
-    weights = chosen scores / their sum * scale."""
+    [T, top]): scores (``scores``: "sigmoid", or "softmax" over all experts), choice by score + correction among the
+    experts of the ``keep`` best of ``groups`` groups (``group_score``: a group counts by the sum of its two largest
+    choice scores, "top2", or by its largest, "max"), weights = chosen scores / their sum * scale, or with
+    ``normalize`` False the chosen scores * scale as they are."""
+    if scores not in ("sigmoid", "softmax") or group_score not in ("top2", "max"):
+        raise KernelError(f"router: scores {scores!r} (sigmoid, softmax) / group score {group_score!r} (top2, max) not built")
     _dev(z, "router logits")
     if z.dtype != torch.float32 or z.dim() != 2 or z.shape[1] < experts:
         raise KernelError(f"router logits must be float32 [T, >= {experts}], are {z.dtype} {tuple(z.shape)}")
@@ -890,7 +924,8 @@ def moe_route(z: torch.Tensor, correction: torch.Tensor | None, *, experts: int,
     chosen = torch.empty((t, top), dtype=torch.int32, device=z.device)
     weight = torch.empty((t, top), dtype=torch.float32, device=z.device)
     check(lib().psb_moe_route(z.data_ptr(), z.shape[1], _ptr(correction), chosen.data_ptr(), weight.data_ptr(), t, experts, top,
-                              groups, keep, float(scale), _stream()), "moe_route")
+                              groups, keep, float(scale), 1 if scores == "softmax" else 0, 1 if group_score == "max" else 0,
+                              1 if normalize else 0, _stream()), "moe_route")
     return chosen, weight
 
 
@@ -900,16 +935,26 @@ MOE_TCGEN05_MIN_PAIRS = 256   # with fewer (token, expert) pairs in a step the 6
 
 
 def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, *,
-                activation: str = "relu2", shared: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None,
-                out_dtype: torch.dtype | None = None) -> torch.Tensor:
+                activation: str | None = "relu2", shared: torch.Tensor | None = None, shared_gate: torch.Tensor | None = None,
+                out_dtype: torch.dtype | None = None, glu: tuple[float, float, float] | None = None) -> torch.Tensor:
     """sum over a token's chosen experts of weight * down_e(act(up_e x)) (+ sigmoid(shared_gate) * shared), for
-    w_up [E, ff, H], w_down [E, H, ff].  ``shared_gate``: float32 column view [T, 1] (its row stride may be wider)."""
+    w_up [E, ff, H], w_down [E, H, ff].  ``shared_gate``: float32 column view [T, 1] (its row stride may be wider);
+    without it the shared expert's output is added as it is.
+
+    ``glu`` = (limit, alpha, offset): gated experts.  w_up is then [E, 2 ff, H], an expert's gate rows followed by its
+    up rows, ``activation`` is None, and between the two products g * sigmoid(alpha g) * (u + offset) is taken with
+    g = min(gate, limit), u = clamp(up, -limit, limit)."""
     _dev(x, "expert input"), _dev(w_up, "expert up matrices"), _dev(w_down, "expert down matrices")
     _i32(chosen, "chosen experts"), _dev(weight, "expert weights")
     t, h = x.shape
     e, ff, _ = w_up.shape
     top = chosen.shape[1]
-    if tuple(w_up.shape) != (e, ff, h) or tuple(w_down.shape) != (e, h, ff) or tuple(weight.shape) != (t, top) or weight.dtype != torch.float32:
+    ff_in = ff  # columns of the first product
+    if glu is not None:
+        if activation is not None or ff % 2:
+            raise KernelError("gated experts: the gate is the activation, and the first matrices hold gate rows and up rows")
+        ff = ff // 2
+    if tuple(w_up.shape) != (e, ff_in, h) or tuple(w_down.shape) != (e, h, ff) or tuple(weight.shape) != (t, top) or weight.dtype != torch.float32:
         raise KernelError(f"experts: up {tuple(w_up.shape)}, down {tuple(w_down.shape)}, weights {tuple(weight.shape)} do not fit {t} tokens of {h}")
     if activation not in MOE_ACTIVATIONS:
         raise KernelError(f"experts: activation {activation!r} is not built (one of {sorted(k for k in MOE_ACTIVATIONS if k)})")
@@ -931,17 +976,23 @@ def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, w_u
         sms = _sms(dev)
         rows = torch.empty((room, h), dtype=torch.bfloat16, device=dev)
         check(lib().psb_moe_gather(x.data_ptr(), row_pair.data_ptr(), rows.data_ptr(), room, h, top, _stream()), "moe_gather")
-        mid = torch.empty((room, ff), dtype=torch.bfloat16, device=dev)
-        check(lib().psb_gemm_tcgen05_grouped(rows.data_ptr(), w_up.data_ptr(), mid.data_ptr(), room, ff, h, e, tile_expert.data_ptr(),
+        mid = torch.empty((room, ff_in), dtype=torch.bfloat16, device=dev)
+        check(lib().psb_gemm_tcgen05_grouped(rows.data_ptr(), w_up.data_ptr(), mid.data_ptr(), room, ff_in, h, e, tile_expert.data_ptr(),
                                              MOE_ACTIVATIONS[activation], sms, _stream()), "gemm_tcgen05_grouped")
+        if glu is not None:
+            mid = clipped_glu(mid, *glu)
         y = torch.empty((room, h), dtype=torch.bfloat16, device=dev)
         check(lib().psb_gemm_tcgen05_grouped(mid.data_ptr(), w_down.data_ptr(), y.data_ptr(), room, h, ff, e, tile_expert.data_ptr(),
                                              0, sms, _stream()), "gemm_tcgen05_grouped")
     else:
-        mid = torch.empty((room, ff), dtype=x.dtype, device=dev)
+        mid = torch.empty((room, ff_in), dtype=x.dtype, device=dev)
+        if glu is not None:
+            mid.zero_()  # rows that belong to nobody are not written by the product, and the gate reads every row
         check(lib().psb_moe_gemm(x.data_ptr(), _code(x, "expert input"), w_up.data_ptr(), _code(w_up, "expert up matrices"), mid.data_ptr(),
-                                 _code(mid, "expert activations"), offsets.data_ptr(), row_pair.data_ptr(), room, e, ff, h, top, 1,
+                                 _code(mid, "expert activations"), offsets.data_ptr(), row_pair.data_ptr(), room, e, ff_in, h, top, 1,
                                  MOE_ACTIVATIONS[activation], _stream()), "moe_gemm")
+        if glu is not None:
+            mid = clipped_glu(mid, *glu)
         y = torch.empty((room, h), dtype=torch.float32, device=dev)
         check(lib().psb_moe_gemm(mid.data_ptr(), _code(mid, "expert activations"), w_down.data_ptr(), _code(w_down, "expert down matrices"),
                                  y.data_ptr(), F32, offsets.data_ptr(), row_pair.data_ptr(), room, e, h, ff, top, 0, 0, _stream()), "moe_gemm")
@@ -1029,16 +1080,45 @@ def attention_prepare(proj: torch.Tensor, kv: torch.Tensor, table: torch.Tensor,
                       dim: int, vdim: int, page_size: int, cos: torch.Tensor | None = None, sin: torch.Tensor | None = None,
                       rotary_dim: int | None = None, interleaved: bool = False, unit_norm_eps: float | None = None,
                       head_factor: torch.Tensor | None = None, values_are_keys: bool = False,
-                      split_planes: bool = False) -> torch.Tensor:
+                      split_planes: bool = False, bias: torch.Tensor | None = None, write_kv: bool = True) -> torch.Tensor:
     """One pass over the fused projection [T, q | k | v] (or [T, q | k] with ``values_are_keys``): optional rotation of
     the first ``rotary_dim`` elements of query and key heads by position (``cos``/``sin`` float32 [positions,
     rotary_dim/2]), optional division of every query and key head by its root mean square (``unit_norm_eps``), an
     optional float32 factor per query head; keys and values appended to the cache entry [pages, 1, hkv, page_size,
     dim + vdim], or with ``split_planes`` (vdim == dim) [pages, 2, hkv, page_size, dim]: keys in plane 0, values in
-    plane 1.  Returns the queries [T, hq, dim]."""
-    _dev(kv, "cache entry"), _i32(table, "page table")
+    plane 1.  Returns the queries [T, hq, dim].
+
+    ``bias`` (float32, one number per column of the projection): added to the projection in float32 before anything
+    else.  ``write_kv`` False: the projection holds queries only and nothing is appended (a layer that reads the keys
+    and values another layer has stored); ``kv`` and ``table`` may then be None."""
     t = proj.shape[0]
-    want = num_heads * dim + num_kv_heads * dim + (0 if values_are_keys else num_kv_heads * vdim)
+    want = num_heads * dim + (num_kv_heads * dim + (0 if values_are_keys else num_kv_heads * vdim) if write_kv else 0)
+    if bias is not None:
+        _f32_vector(bias, want, "projection bias")
+    if not write_kv:
+        if not proj.is_cuda or proj.dim() != 2 or proj.shape[1] != want or proj.stride(1) != 1:
+            raise KernelError(f"query projection must be [T, {want}] on the device, is {tuple(proj.shape)}")
+        max_pos = 0
+        rotary_dim = dim if rotary_dim is None else int(rotary_dim)
+        if cos is not None:
+            if sin is None or cos.shape != sin.shape or cos.dtype != torch.float32 or cos.dim() != 2 or cos.shape[1] != rotary_dim // 2 \
+                    or rotary_dim % 2 or not 2 <= rotary_dim <= dim:
+                raise KernelError(f"angle tables must be float32 [positions, {rotary_dim // 2}] for {rotary_dim} rotated elements of {dim}")
+            _dev(cos, "cosines"), _dev(sin, "sines")
+            max_pos = cos.shape[0]
+            if ctx.max_kv_len > max_pos:
+                raise KernelError(f"a position of this step ({ctx.max_kv_len - 1}) lies beyond the angle tables ({max_pos} positions)")
+        if head_factor is not None:
+            _f32_vector(head_factor, num_heads, "per-head factors")
+        q = torch.empty((t, num_heads, dim), dtype=proj.dtype, device=proj.device)
+        check(lib().psb_attention_prepare(proj.data_ptr(), int(proj.stride(0)), _code(proj, "projection output"), _i32(ctx.positions, "positions").data_ptr(),
+                                          _i32(ctx.token_item, "token-to-item map").data_ptr(), None, 0, _ptr(cos), _ptr(sin),
+                                          _ptr(head_factor), None, _code(proj, "projection output"), q.data_ptr(), t, num_heads, num_kv_heads, dim, vdim,
+                                          1, 0, max_pos, rotary_dim, 1 if interleaved else 0,
+                                          -1.0 if unit_norm_eps is None else float(unit_norm_eps), 0, 0, _ptr(bias), 0, _stream()),
+              "attention_prepare")
+        return q
+    _dev(kv, "cache entry"), _i32(table, "page table")
     if not proj.is_cuda or proj.dim() != 2 or proj.shape[1] != want or proj.stride(1) != 1:
         raise KernelError(f"projection output must be [T, {want}] on the device (rows may be part of wider ones), is {tuple(proj.shape)}")
     entry = (2, num_kv_heads, page_size, dim) if split_planes else (1, num_kv_heads, page_size, dim + vdim)
@@ -1066,7 +1146,7 @@ def attention_prepare(proj: torch.Tensor, kv: torch.Tensor, table: torch.Tensor,
                                       _ptr(cos), _ptr(sin), _ptr(head_factor), kv.data_ptr(), _code(kv, "cache entry"), q.data_ptr(),
                                       t, num_heads, num_kv_heads, dim, vdim, page_size, kv.shape[0], max_pos, rotary_dim,
                                       1 if interleaved else 0, -1.0 if unit_norm_eps is None else float(unit_norm_eps),
-                                      1 if values_are_keys else 0, 1 if split_planes else 0, _stream()), "attention_prepare")
+                                      1 if values_are_keys else 0, 1 if split_planes else 0, _ptr(bias), 1, _stream()), "attention_prepare")
     return q
 
 

@@ -28,8 +28,8 @@ P, I, L, F = c_void_p, c_int, c_int64, c_float
 _SIGNATURES: dict[str, list] = {
     # (ids, table, table_dtype, out_f32, T, H, V, stream)
     "psb_embedding": [P, P, I, P, I, I, I, P],
-    # (h, delta, delta_dtype, weight, rows, x, x_dtype, n_rows, H, eps, update_h, stream)
-    "psb_add_rmsnorm": [P, P, I, P, P, P, I, I, I, F, I, P],
+    # (h, delta, delta_dtype, weight, rows, x, x_dtype, n_rows, H, eps, update_h, delta_scale, delta_shift, stream)
+    "psb_add_rmsnorm": [P, P, I, P, P, P, I, I, I, F, I, P, P, P],
     # (a, a_dtype, w, w_dtype, c, c_dtype, M, N, K, lda, ldw, ldc, accumulate, stream)
     "psb_gemm_nt": [P, I, P, I, P, I, I, I, I, L, L, L, I, P],
     # (qkv, dtype, positions, token_item, cos, sin, table, table_width, kv, kv_dtype, q_out,
@@ -134,6 +134,8 @@ _SIGNATURES: dict[str, list] = {
     "psb_gated_norm_add": [P, P, I, P, I, P, P, P, I, I, I, F, F, P],
     # (x, dtype, out, total, code, params, stream)
     "psb_unary_act": [P, I, P, L, I, P, P],
+    # (x, x_dtype, gate_f32, out, out_dtype, total, stream)
+    "psb_gate_mul": [P, I, P, P, I, L, P],
     # (proj, dtype, positions, token_item, table, table_width, cos, sin, gain_q, gain_kv, cq_out, gate_out, cache, cache_dtype,
     #  T, q_rank, rank, rot, rot_dims, heads, page_size, num_pages, max_positions, eps, stream)
     "psb_latent_prepare": [P, I, P, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
@@ -141,7 +143,7 @@ _SIGNATURES: dict[str, list] = {
     "psb_latent_query_rotate": [P, I, P, P, P, P, I, I, I, I, I, I, I, P],
     # (q_lat, cache, cache_dtype, table, table_width, positions, token_item, gate, out, out_dtype, T, heads, rank, rot,
     #  page_size, num_pages, window, scale, heads_per_block, splits, partial, stream)
-    "psb_latent_attention": [P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P],
+    "psb_latent_attention": [P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P],
     # (cache_dtype, rank, rot) -> 1 if the kernel that reads rows side by side takes the case
     "psb_latent_attention_rows_supported": [I, I, I],
     "psb_latent_attention_max_rank": [],
@@ -167,14 +169,14 @@ _SIGNATURES: dict[str, list] = {
     "psb_attention_biased_append": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, P],
     # (q, dtype, kv, kv_dtype, table, table_width, positions, token_item, bias, sink, out, T, hq, hkv, dim, vdim, page_size,
     #  window, chunk, reach, scale, item_start, skip_from, stream)
-    "psb_attention_biased": [P, I, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, I, P],
+    "psb_attention_biased": [P, I, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, I, I, P],
     "psb_attention_biased_tile_tokens": [],
     "psb_attention_biased_tile_supported": [I, I, I, I],
     # (q, kv, table, table_width, positions, item_start, items, T, min_tokens, bias, sink, out, hq, hkv, dim, vdim,
     #  page_size, window, chunk, reach, scale, stream)
-    "psb_attention_biased_tiles": [P, P, P, I, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "psb_attention_biased_tiles": [P, P, P, I, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "psb_attention_biased_mma_supported": [I, I, I, I],
-    "psb_attention_biased_mma": [P, P, P, I, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "psb_attention_biased_mma": [P, P, P, I, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "psb_delta_max_taps": [],
     # (proj, dtype, ba, taps, a_log, dt_bias, state, positions, token_item, item_start, slots, qkv_out, bd_out, T, G, H, dim,
     #  vdim, K, num_slots, slot_floats, stream)
@@ -184,7 +186,7 @@ _SIGNATURES: dict[str, list] = {
     # (o, proj, dtype, gain, out, T, G, H, dim, vdim, eps, stream)
     "psb_delta_finish": [P, P, I, P, P, I, I, I, I, I, F, P],
     # (z, ldz, correction, chosen, weight, T, E, top, groups, keep, scale, stream)
-    "psb_moe_route": [P, I, P, P, P, I, I, I, I, I, F, P],
+    "psb_moe_route": [P, I, P, P, P, I, I, I, I, I, F, I, I, I, P],
     # (chosen, offsets, row_pair, pair_row, tile_expert, pairs, E, pad, rows_room, stream)
     "psb_moe_group": [P, P, P, P, P, I, I, I, I, P],
     # (x, row_pair, out, rows, K, top, stream)
@@ -203,7 +205,7 @@ _SIGNATURES: dict[str, list] = {
     "psb_normed_pair_sum": [P, P, I, P, P, P, I, I, F, F, P],
     # (proj, ld, dtype, positions, token_item, table, table_width, cos, sin, head_factor, kv, kv_dtype, q_out, T, hq, hkv, dim, vdim,
     #  page_size, num_pages, max_positions, rotary_dim, interleaved, eps, values_are_keys, split_planes, stream)
-    "psb_attention_prepare": [P, L, I, P, P, P, I, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P],
+    "psb_attention_prepare": [P, L, I, P, P, P, I, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P, I, P],
     # (proj, ld, dtype, bias_z, bias_x, state, stride, item_start, slots, carry, start, out, items, T, W, num_slots, chunk,
     #  two_pass, stream)
     "psb_min_gru": [P, L, I, P, P, P, L, P, P, P, P, P, I, I, I, I, I, I, P],

@@ -40,6 +40,24 @@ class PagedKV:
     # Chunked attention: a query sees only keys of its own run of ``chunk`` positions (runs counted from position 0), so
     # the pages before the run of the next token are never read again and go back to the pool like pages behind a window.
     chunk: int | None = None
+    # With a window: the first ``keep_first`` keys of a sequence stay readable by every later query, so their pages are
+    # never given back while the request lives; the pages between them and the window are.
+    keep_first: int = 0
+
+    def same_layout(self, other: "PagedKV") -> bool:
+        """Whether two needs describe the same rows in the pages (they may differ in how far back they read)."""
+        return (self.num_kv_heads, self.head_dim, self.key_order, self.planes) == \
+               (other.num_kv_heads, other.head_dim, other.key_order, other.planes)
+
+    def reach_of_both(self, other: "PagedKV") -> "PagedKV":
+        """The need of an entry that this need writes and ``other`` also reads: nothing either still reads is let go."""
+        import dataclasses
+        window = None if self.window is None or other.window is None else max(self.window, other.window)
+        chunk = self.chunk if self.chunk == other.chunk else None
+        if chunk is None and (self.chunk is not None or other.chunk is not None):
+            window = None  # a chunk mask on one side only: keep everything
+        keep = max(self.keep_first, other.keep_first) if window is not None else 0
+        return dataclasses.replace(self, window=window, chunk=chunk, keep_first=keep)
 
 
 @dataclass(frozen=True)

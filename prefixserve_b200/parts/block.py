@@ -3,7 +3,9 @@
 The arrangement is chosen by name per layer.  Built in:
 
 ``pre_norm``: x = norm(h); h += mixer(x); x = norm(h); h += ffn(x)
-(prefixserve/model/llama.py:112-121, the only one that architecture uses).
+(prefixserve/model/llama.py:112-121, the only one that architecture uses).  With ``mixer_scale`` / ``ffn_scale`` in
+the layer's description the sublayer's result is multiplied by a learned vector, channel by channel, before the sum:
+h += scale_1 * mixer(x); h += scale_2 * ffn(x).
 ``parallel``: both sublayers read the same stream, h += mixer(norm_a(h)) + ffn(norm_b(h)).
 ``gated_post_norm``: the sublayers read the stream itself and the norm sits on their result, behind a gate computed
 from the same input: h += scale * norm_a(mixer(h) * sigmoid(gate_a(h))); then the same with the feed-forward.
@@ -51,6 +53,10 @@ class Block:
         self.residual_scale = float(spec.residual_scale)
         self.mixer_post_norm = make("norm", spec.mixer_post_norm) if spec.mixer_post_norm is not None else None
         self.ffn_post_norm = make("norm", spec.ffn_post_norm) if spec.ffn_post_norm is not None and spec.ffn is not None else None
+        self.mixer_scale = make("gate", spec.mixer_scale) if spec.mixer_scale is not None else None
+        self.ffn_scale = make("gate", spec.ffn_scale) if spec.ffn_scale is not None and spec.ffn is not None else None
+        if (self.mixer_scale is not None or self.ffn_scale is not None) and spec.arrangement != "pre_norm":
+            raise ValueError("a channel scale on a sublayer's result goes with the pre_norm arrangement")
 
     def named_parts(self):
         parts = [("mixer_norm", self.mixer_norm), ("mixer", self.mixer)]
@@ -58,12 +64,16 @@ class Block:
             parts.append(("mixer_post_norm", self.mixer_post_norm))
         if self.mixer_gate is not None:
             parts.append(("mixer_gate", self.mixer_gate))
+        if self.mixer_scale is not None:
+            parts.append(("mixer_scale", self.mixer_scale))
         if self.ffn is not None:
             parts += [("ffn_norm", self.ffn_norm), ("ffn", self.ffn)]
             if self.ffn_post_norm is not None:
                 parts.append(("ffn_post_norm", self.ffn_post_norm))
             if self.ffn_gate is not None:
                 parts.append(("ffn_gate", self.ffn_gate))
+            if self.ffn_scale is not None:
+                parts.append(("ffn_scale", self.ffn_scale))
         return tuple(parts)
 
     def forward(self, h, pending, ctx: StepContext, cache: CacheView):
@@ -82,8 +92,12 @@ def _sublayer(norm, part, h, pending, ctx, *more):
 
 def pre_norm(block: Block, h, pending, ctx: StepContext, cache: CacheView):
     h, pending = _sublayer(block.mixer_norm, block.mixer, h, pending, ctx, cache)
+    if block.mixer_scale is not None:  # joins the stream as pending * scale, in the next norm's kernel
+        pending = ops.Affine(pending, scale=block.mixer_scale.weight)
     if block.ffn is not None:
         h, pending = _sublayer(block.ffn_norm, block.ffn, h, pending, ctx)
+        if block.ffn_scale is not None:
+            pending = ops.Affine(pending, scale=block.ffn_scale.weight)
     return h, pending
 
 

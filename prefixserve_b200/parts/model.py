@@ -78,8 +78,14 @@ class DecoderModel:
         for call in self.spec.schedule:
             if not call.writes_cache:
                 need = self.blocks[call.layer].mixer.cache_need()
-                if needs[call.cache] != need:
-                    raise ValueError(f"layer {call.layer} reads cache entry {call.cache} but needs {need}, entry holds {needs[call.cache]}")
+                held = needs[call.cache]
+                if held != need:
+                    # a reader with a mask of its own (another window, other kept keys) is fine as long as the rows are
+                    # laid out alike: the entry then keeps whatever either of them can still read
+                    if (held is None or held.paged is None or need.paged is None or held.state != need.state
+                            or not held.paged.same_layout(need.paged)):
+                        raise ValueError(f"layer {call.layer} reads cache entry {call.cache} but needs {need}, entry holds {held}")
+                    needs[call.cache] = CacheNeed(paged=held.paged.reach_of_both(need.paged), state=held.state)
         needs = [n if n is not None else CacheNeed() for n in needs]
         if getattr(self.embedding, "uses_step", False):  # an embedding that carries something per request: the entry after the layers'
             needs.append(self.embedding.cache_need())

@@ -6,6 +6,10 @@ frequencies 1/theta^(2j/D); with llama3 scaling, wavelengths longer than
 original/low_freq_factor are divided by ``factor``, those shorter than
 original/high_freq_factor are kept, and the band between is blended.  The
 tables hold D/2 columns (the reference's table repeats them to D).
+With ``yarn`` scaling (factor, original_max_positions, fast, slow) the pair index at which a wavelength makes t turns
+over the original length is d(t) = D ln(original / (2 pi t)) / (2 ln theta); pairs below lo = max(floor(d(fast)), 0)
+keep their frequency, pairs above hi = min(ceil(d(slow)), D - 1) have it divided by ``factor``, with a linear ramp
+between (clamp((j - lo) / max(hi - lo, 0.001), 0, 1)); cosines and sines are multiplied by 0.1 ln(factor) + 1.
 ``none``: no rotation; queries and keys go through unchanged.
 
 What a rotating part tells its mixer: ``cos``/``sin`` float32 [positions,
@@ -26,14 +30,31 @@ from .base import PositionEncoding
 from .registry import register_position
 
 
+def rope_amplitude(scaling) -> float:
+    """What cosines and sines are multiplied by: 0.1 ln(factor) + 1 under yarn scaling, else 1."""
+    if scaling and scaling.get("kind") == "yarn":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
+
+
 def rope_inverse_frequencies(head_dim: int, theta: float, scaling) -> torch.Tensor:
     exponents = torch.arange(0, head_dim, 2, dtype=torch.int64).float() / head_dim
     inv = 1.0 / (theta ** exponents)
     if not scaling:
         return inv
     kind = scaling.get("kind")
+    if kind == "yarn":
+        factor, original = float(scaling["factor"]), float(scaling["original_max_positions"])
+
+        def pair_of(turns: float) -> float:
+            return head_dim * math.log(original / (2 * math.pi * turns)) / (2 * math.log(theta))
+
+        lo = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(pair_of(float(scaling["slow"]))), head_dim - 1)
+        ramp = ((torch.arange(head_dim // 2, dtype=torch.float32) - lo) / max(hi - lo, 0.001)).clamp(0, 1)
+        return inv / factor * ramp + inv * (1 - ramp)
     if kind != "llama3":
-        raise ValueError(f"rope scaling kind {kind!r} is not built")
+        raise ValueError(f"rope scaling kind {kind!r} is not built (llama3, yarn)")
     factor = float(scaling["factor"])
     low, high = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
     original = float(scaling["original_max_positions"])
@@ -73,7 +94,11 @@ class RotaryEncoding(PositionEncoding):
         if held is None or held[0].shape[0] < max_positions:
             inv = rope_inverse_frequencies(self.rotary_dim, self.theta, self.scaling)
             angles = torch.outer(torch.arange(max_positions, dtype=torch.int64).float(), inv)  # float32, on the host
-            held = (angles.cos().to(device).contiguous(), angles.sin().to(device).contiguous())
+            amplitude = rope_amplitude(self.scaling)
+            cos, sin = angles.cos(), angles.sin()
+            if amplitude != 1.0:
+                cos, sin = cos * amplitude, sin * amplitude
+            held = (cos.to(device).contiguous(), sin.to(device).contiguous())
             _TABLES[key] = held
         self.cos, self.sin = held
 
