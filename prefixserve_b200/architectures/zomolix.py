@@ -45,9 +45,11 @@ def _writer_of(cfg: ZomolixConfig, i: int) -> int:
 def _mixer_spec(cfg: ZomolixConfig, i: int):
     m = cfg.layers[i].mixer
     if isinstance(m, AttentionConfig):
-        # layers that share a cache entry agree on its layout: rows as soon as one of them keeps first keys
+        # Layers that share a cache entry agree on its layout: a row per token as soon as one of them has a window.  The
+        # kernels that read planes of keys and values know no kept first keys, and behind a window they multiply
+        # whatever a page that has gone back to the pool holds by a weight of zero, which the kernels over rows never read.
         sharing = [l.mixer for j, l in enumerate(cfg.layers) if isinstance(l.mixer, AttentionConfig) and _writer_of(cfg, j) == _writer_of(cfg, i)]
-        rows = any(s.window is not None and s.keep_first > 0 for s in sharing)
+        rows = any(s.window is not None for s in sharing)
         return part("unit_norm_attention", hidden_size=cfg.width, num_heads=m.heads, num_kv_heads=m.kv_heads, dim=m.dim, vdim=m.vdim,
                     scale=m.scale, eps=None, position=_position(m.rot, m.dim, "half"), head_temperature=False, sink=None,
                     values="projected", window=m.window, keep_first=m.keep_first, bias=True, own_kv=m.kv_from is None,

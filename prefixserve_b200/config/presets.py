@@ -136,6 +136,50 @@ PRESETS.update({
 })
 
 
+def _zomolix(width: int, vocab: int, groups: int, heads: int, kv_heads: int, dim: int, latent_heads: int, kv_rank: int,
+             window: int, experts: int, top: int, ff: int, shared_ff: int) -> dict:
+    """``groups`` times (latent attention, windowed attention, latent attention, windowed attention reading the keys and
+    values of the one before it), every layer with routed experts and a shared one."""
+    rot = {"base": 500000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    lrot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    mlp = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top, "groups": {"count": 8, "keep": 4}},
+           "shared": {"ff": shared_ff, "limit": 7.0}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": latent_heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": kv_rank, "scale": 192 ** -0.5, "rot": lrot}}
+    layers = []
+    for g in range(groups):
+        attention = {"type": "attention", "mlp": mlp,
+                     "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": rot,
+                               "mask": {"size": window, "keep_first": 4}}}
+        reader = {"type": "attention", "mlp": mlp, "mixer": dict(attention["mixer"], kv_from=4 * g + 1)}
+        layers += [latent, attention, latent, reader]
+    return {"architecture": "Zomolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "layers": layers}
+
+
+PRESETS.update({
+    "zomolix-tiny": {
+        "architecture": "Zomolix", "vocab": 256, "width": 64, "norm": {"eps": 1e-6}, "embedding": {"scale": 2.0},
+        "layers": [
+            {"type": "latent_attention",
+             "mlp": {"kind": "moe", "expert": {"ff": 32, "limit": 2.0}, "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}},
+                     "shared": {"ff": 48, "limit": 1.5}},
+             "mixer": {"heads": 2, "dim": 16, "rot_dim": 8, "vdim": 24, "kv_rank": 32, "scale": 0.2,
+                       "rot": {"base": 10000.0, "dims": 8, "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}}}},
+            {"type": "attention", "mlp": None,
+             "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.25, "mask": {"size": 24, "keep_first": 3},
+                       "rot": {"base": 10000.0, "dims": 8}}},
+            {"type": "attention",
+             "mlp": {"kind": "moe", "expert": {"ff": 16, "limit": 3.0}, "router": {"experts": 4, "top": 1, "groups": {"count": 1, "keep": 1}}},
+             "mixer": {"heads": 2, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.25, "mask": {"size": 40, "keep_first": 0},
+                       "rot": {"base": 10000.0, "dims": 8}, "kv_from": 1}},
+        ],
+    },
+    # layer sizes of a 1B- and an 8B-class decoder (width, heads), for the benchmarks: per token 4 of 32 experts and a shared one
+    "zomolix-2048": _zomolix(2048, 32768, 3, 16, 4, 128, 16, 512, 1024, 32, 4, 1024, 1024),
+    "zomolix-4096": _zomolix(4096, 32768, 2, 32, 8, 128, 32, 512, 2048, 32, 4, 2048, 2048),
+})
+
+
 def preset(name: str):
     """The typed configuration of a preset, read by its architecture's own reader."""
     try:

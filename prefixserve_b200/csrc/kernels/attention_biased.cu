@@ -317,9 +317,10 @@ attention_biased_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
       if (keep_first > 0 && lo <= keep_first) lo = 0;
       // (a tile whose first token still reaches the kept keys has no kept runs, but a later token's window may
       // already start beyond them: such a token sees the kept keys inside the ordinary runs)
-      if (!kept && base + 31 < lo && base >= keep_first) continue;
+      const bool inline_kept = kept_runs == 0 && keep_first > 0;  // the kept keys lie inside the ordinary runs
+      if (!kept && base + 31 < lo && !(inline_kept && base < keep_first)) continue;
       const int key = base + lane;
-      const bool live = kept ? key < keep_first : (key <= p && (key >= lo || key < keep_first));
+      const bool live = kept ? key < keep_first : (key <= p && (key >= lo || (inline_kept && key < keep_first)));
       float s = -FLT_MAX;
       if (live) {
         const float* qq = qs + (size_t)u * DP;
@@ -340,7 +341,7 @@ attention_biased_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
 #pragma unroll
       for (int i = 0; i < VP / 32; ++i) a[i] = acc[lane + 32 * i] * alpha;
       const int n_live = kept ? min(32, keep_first - base) : min(32, p - base + 1);
-      const int j0 = (kept || base < keep_first) ? 0 : max(0, lo - base);
+      const int j0 = (kept || (inline_kept && base < keep_first)) ? 0 : max(0, lo - base);
       for (int j = j0; j < n_live; ++j) {
         const float pj = __shfl_sync(0xffffffffu, pr, j);
 #pragma unroll
@@ -518,7 +519,9 @@ attention_biased_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1, key = base + n * 8 + 2 * tig + (e & 1);
         float v = -INFINITY;
-        if (kept ? key < keep_first : (key <= pos[r] && (key >= low[r] || key < keep_first))) {
+        // (without kept blocks of their own the kept keys lie inside the ordinary blocks: a later row of the tile may
+        // see them although its window starts beyond them)
+        if (kept ? key < keep_first : (key <= pos[r] && (key >= low[r] || (kept_blocks == 0 && key < keep_first)))) {
           v = sc[n][e] * scale;
           if (brow) {
             const int far = min(pos[r] - key, reach - 1);
