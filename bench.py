@@ -770,7 +770,10 @@ GEKOPEL_SIZES = {"2048": ("gekopel-2048", "nerenex-2048"), "4096": ("gekopel-409
 # --workload goganex: the closest model already here is the Llama (attention over every earlier key with a rotation, a gated
 # feed-forward, pre-norm blocks), at the same width, heads, feed-forward size and number of layers
 GOGANEX_SIZES = {"2048": ("goganex-2048", "1b"), "4096": ("goganex-4096", "8b")}
-BESIDE = {"nerenex": "llama", "gekopel": "nerenex", "goganex": "llama"}
+# --workload zomolix: the closest model already here is Gekopel (routed experts with a shared one behind every mixer, attention
+# over a bounded span of keys read from a row per token, a sink in a softmax), at the same width and with as many experts
+ZOMOLIX_SIZES = {"2048": ("zomolix-2048", "gekopel-2048"), "4096": ("zomolix-4096", "gekopel-4096")}
+BESIDE = {"nerenex": "llama", "gekopel": "nerenex", "goganex": "llama", "zomolix": "gekopel"}
 
 
 def run_nerenex(args, design: str = "nerenex") -> dict:
@@ -782,7 +785,10 @@ def run_nerenex(args, design: str = "nerenex") -> dict:
     and a sink; routed experts; sandwich-norm blocks) beside Nerenex at the same width and number of layers.
     --workload goganex: the same for the Goganex design (token shift; unit-normed attention with a factor per head and a
     sink, three layers of it, then attention whose keys are its values beside a minGRU; clipped gated feed-forward)
-    beside a Llama of the same width and number of layers."""
+    beside a Llama of the same width and number of layers.
+    --workload zomolix: the same for the Zomolix design (latent attention with a sink and an output gate; windowed attention
+    with biases and kept first keys, every other one reading its predecessor's keys and values; routed gated experts with
+    a shared one; a learned scale per channel on every sublayer) beside Gekopel at the same width."""
     import re
 
     import numpy as np
@@ -795,7 +801,7 @@ def run_nerenex(args, design: str = "nerenex") -> dict:
 
     prompt, context, batches = 2048, args.context if "--context" in sys.argv else 2048, (8, 32)
     steps, warmup = min(args.steps, 32), max(3, min(args.warmup, 8))
-    sizes = {"gekopel": GEKOPEL_SIZES, "goganex": GOGANEX_SIZES}.get(design, NERENEX_SIZES)
+    sizes = {"gekopel": GEKOPEL_SIZES, "goganex": GOGANEX_SIZES, "zomolix": ZOMOLIX_SIZES}.get(design, NERENEX_SIZES)
     out = {"workload": design, "dtype": "bf16", "data": "synthetic", "prompt": prompt, "context": context, "steps": steps,
            "warmup": warmup, "timing": "CUDA events; weights of every model exceed L2", "peaks": peaks(), "sizes": {}}
     for size in ([args.model] if args.model in sizes else sorted(sizes)):
@@ -806,7 +812,7 @@ def run_nerenex(args, design: str = "nerenex") -> dict:
             if which == design:
                 cfg = preset(own_name)
                 vocab = cfg.vocab
-            elif which == "nerenex":
+            elif which in ("nerenex", "gekopel"):
                 cfg = preset(llama_name)
                 vocab = cfg.vocab
             else:
@@ -878,7 +884,7 @@ def run_nerenex(args, design: str = "nerenex") -> dict:
                     prefill_once()
                 with ClockSampler() as clocks:
                     times = sorted(prefill_once() for _ in range(5))
-                res = {"weight_bytes": engine.weight_bytes(), "layers": n_layers,
+                res = {"weight_bytes": engine.weight_bytes(), "layers": len(cfg.layers) if hasattr(cfg, "layers") else n_layers,
                        "prefill_ms": round(times[2], 3), "prefill_tok_s": round(prompt / times[2] * 1e3, 1), "clocks": clocks.summary()}
                 res["prefill_kernels"] = kernels_of(prefill_once)
                 for b in batches:
@@ -953,11 +959,12 @@ def main() -> int:
     p.add_argument("--profile", action="store_true",
                    help="--timeline plus, per kernel, the bytes and flops it has to do in the step and the fraction of the "
                         "measured peak that its time inside the step amounts to")
-    p.add_argument("--workload", choices=["decode", "shared-prefix", "mixed", "nerenex", "gekopel", "goganex"], default="decode",
+    p.add_argument("--workload", choices=["decode", "shared-prefix", "mixed", "nerenex", "gekopel", "goganex", "zomolix"], default="decode",
                    help="decode: the headline line.  shared-prefix: 64 requests over 4 system prefixes through the entry "
                         "point, prefix cache on and off.  mixed: steps of one 512-token prompt portion beside 64 decoded tokens.  "
                         "nerenex: prefill and decode of the Nerenex design beside a Llama of the same width and depth (--model 2048|4096).  "
-                        "gekopel: the same for the Gekopel design beside Nerenex.  goganex: the same for the Goganex design beside a Llama")
+                        "gekopel: the same for the Gekopel design beside Nerenex.  goganex: the same for the Goganex design beside a Llama.  "
+                        "zomolix: the same for the Zomolix design beside Gekopel")
     p.add_argument("--model", choices=sorted(SIZES) + sorted(NERENEX_SIZES), default=None,
                    help="layer sizes for --workload shared-prefix (8b) / mixed (3b), and for --only decode (the headline stays 1b)")
     p.add_argument("--requests", type=int, default=64, help="requests of --workload shared-prefix")
@@ -993,7 +1000,7 @@ def main() -> int:
             return 0
         if _no_device(args):
             return 1
-        if args.workload in ("nerenex", "gekopel", "goganex"):
+        if args.workload in ("nerenex", "gekopel", "goganex", "zomolix"):
             result = run_nerenex(args, args.workload)
             print(json.dumps(result))
             return 0

@@ -78,7 +78,8 @@ __device__ __forceinline__ float clipped_gate(float g, float u, const GluArgs& a
 //
 // Grouped products (``tile_expert`` given): W is a stack of matrices [experts * N_out, K] and every 128-row tile of A
 // belongs to one of them, named by tile_expert[row tile] (-1: the tile holds no rows and is skipped by all three
-// roles alike); the W rows of the tile start at expert * N_out.  Columns of a tile beyond N_out read the next matrix's
+// roles alike); the W rows of the tile start at expert * N_out (gated: at expert * 2 N_out, the expert's gate rows
+// followed by its up rows).  Columns of a tile beyond N_out read the next matrix's
 // rows and are never stored.
 
 // One thread's row of a 128 x BN tile of sums, for the projection of an attention layer: 16 columns are 8 pairs of one
@@ -212,7 +213,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (tile_expert) {
           const int expert = tile_expert[tile % m_blocks];
           if (expert < 0) continue;
-          n0 += expert * N_out;
+          n0 += expert * (gated ? 2 * N_out : N_out);  // a gated expert holds its gate rows, then its up rows
         }
         const int n1 = gated ? up_offset + n0 : n0 + BN_HALF;
         for (int kb = 0; kb < k_blocks; ++kb) {
@@ -482,6 +483,18 @@ PSB_API int psb_gemm_tcgen05_grouped(const void* a, const void* w, void* c, int 
   if (experts < 1 || !tile_expert) PSB_REFUSE("gemm_tcgen05_grouped: needs the experts and the tiles' experts");
   if ((long long)experts * N > 0x7fffffffLL) PSB_REFUSE("gemm_tcgen05_grouped: too many rows in the stack of matrices");
   return launch(a, w, c, M, experts * N, N, K, 0, relu2 ? MODE_RELU2 : MODE_PLAIN, sms, stream, RopeArgs{}, (const int32_t*)tile_expert);
+}
+
+// Grouped and gated: act[M, I] = g * sigmoid(alpha g) * (u + offset) with g = min(A Wg[e]^T, limit), u = clamp(A Wu[e]^T,
+// -limit, limit) for W = [experts, 2 I, K], an expert's gate rows followed by its up rows; rows of A and tile_expert as above.
+PSB_API int psb_gemm_tcgen05_grouped_gated_clipped(const void* a, const void* w, void* act, int M, int I, int K, int experts,
+                                                   const void* tile_expert, float limit, float alpha, float offset, int sms,
+                                                   cudaStream_t stream) {
+  if (experts < 1 || !tile_expert) PSB_REFUSE("gemm_tcgen05_grouped_gated_clipped: needs the experts and the tiles' experts");
+  if ((long long)experts * 2 * I > 0x7fffffffLL) PSB_REFUSE("gemm_tcgen05_grouped_gated_clipped: too many rows in the stack of matrices");
+  if (!(limit > 0.f)) PSB_REFUSE("gemm_tcgen05_grouped_gated_clipped: the limit must be positive");
+  return launch(a, w, act, M, experts * 2 * I, I, K, I, MODE_GATED_CLIPPED, sms, stream, RopeArgs{}, (const int32_t*)tile_expert,
+                GluArgs{limit, alpha, offset});
 }
 
 // The projection of an attention layer for many tokens: A W^T with W = [queries; keys; values] [(hq + 2 hkv) D, K] in the

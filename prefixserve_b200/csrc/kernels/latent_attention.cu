@@ -562,7 +562,8 @@ constexpr int BAND_PER = 16;
 
 __global__ void __launch_bounds__(128)
 latent_band_softmax_kernel(const float* __restrict__ scores, const int32_t* __restrict__ positions,
-                           __nv_bfloat16* __restrict__ weights, int t0, int heads, int KP, int window, float scale) {
+                           __nv_bfloat16* __restrict__ weights, int t0, int heads, int KP, int window, float scale,
+                           const float* __restrict__ sink) {
   __shared__ float scratch[8];
   pdl_trigger();
   pdl_wait();
@@ -589,6 +590,8 @@ latent_band_softmax_kernel(const float* __restrict__ scores, const int32_t* __re
   if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
   __syncthreads();
   m = fmaxf(fmaxf(scratch[0], scratch[1]), fmaxf(scratch[2], scratch[3]));
+  const float sk = sink ? sink[row % heads] : -FLT_MAX;  // a score per head that joins the denominator without a key
+  m = fmaxf(m, sk);
   __syncthreads();
   float l = 0.f;
   if (held) {
@@ -604,6 +607,7 @@ latent_band_softmax_kernel(const float* __restrict__ scores, const int32_t* __re
   if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = l;
   __syncthreads();
   l = (scratch[0] + scratch[1]) + (scratch[2] + scratch[3]);
+  if (sink) l += expf(sk - m);
   const float inv = 1.f / l;
   __nv_bfloat16* hi = weights + row * 2 * KP;
   __nv_bfloat16* lo = hi + KP;
@@ -788,10 +792,10 @@ PSB_API int psb_split_pairs(const void* x, void* hi, void* lo, long long total, 
 }
 
 PSB_API int psb_latent_band_softmax(const void* scores, const void* positions, void* weights, int t0, int n, int heads, int KP,
-                                    int window, float scale, cudaStream_t stream) {
+                                    int window, float scale, const void* sink, cudaStream_t stream) {
   if (t0 < 0 || n < 1 || heads < 1 || window < 1 || KP < window + n - 1) PSB_REFUSE("latent_band_softmax: bad sizes");
   psb_launch(latent_band_softmax_kernel, dim3((unsigned)((long long)n * heads)), dim3(128), 0, stream, (const float*)scores,
-             (const int32_t*)positions, (__nv_bfloat16*)weights, t0, heads, KP, window, scale);
+             (const int32_t*)positions, (__nv_bfloat16*)weights, t0, heads, KP, window, scale, (const float*)sink);
   PSB_LAUNCH_CHECK("latent_band_softmax");
   return 0;
 }

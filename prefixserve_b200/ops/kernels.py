@@ -601,7 +601,7 @@ BAND_MAX_WINDOW = 8192  # wider windows stay with the kernel that walks the keys
 def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tensor, positions: torch.Tensor,
                      token_item: torch.Tensor, gate: torch.Tensor | None, *, rank: int, page_size: int, window: int | None,
                      scale: float, out_dtype: torch.dtype, items=None, key_hint: int = 0,
-                     sink: torch.Tensor | None = None) -> torch.Tensor:
+                     sink: torch.Tensor | None = None, static_shapes: bool = False) -> torch.Tensor:
     """Softmax attention of latent-space queries [T, heads, rank + rot] (float32) over the cached rows
     [pages, page_size, rank + rot]; returns sum_j p_j c_j times the head's gate, [T, heads, rank].
 
@@ -610,8 +610,12 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tens
     sums as products on the tensor cores, softmax in float32 between them); single tokens and short portions through
     the kernel that walks the keys.  Which form a token takes depends on its portion's length only.
 
+    Without a window the band of a run of tokens is every key up to the run's last token: as wide as the run's own
+    positions say in a step that runs at once, as wide as the step's class of lengths (``key_hint``, with
+    ``static_shapes``) in a step whose launches are captured for later steps of other positions.
+
     ``sink`` (float32 [heads]): a score per head whose exponential joins the softmax denominator once, without a key or
-    a value (every token then walks its keys: the banded form has no sink)."""
+    a value."""
     _dev(q_lat, "latent queries"), _dev(cache, "cache entry")
     _i32(table, "page table"), _i32(positions, "positions"), _i32(token_item, "token-to-item map")
     t, heads, d = q_lat.shape
@@ -623,11 +627,11 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tens
         _f32_vector(sink, heads, "sinks")
     out = torch.empty((t, heads, rank), dtype=out_dtype, device=q_lat.device)
     banded = []
-    if (items is not None and sink is None and window and window <= BAND_MAX_WINDOW and cache.dtype == torch.bfloat16 and d % 8 == 0
-            and rank % 8 == 0):
-        banded = [(it.first_token, it.end - it.start) for it in items if it.end - it.start >= BAND_MIN_TOKENS]
+    reach = window or (key_hint if static_shapes else max((it.end for it in items), default=0) if items is not None else 0)
+    if (items is not None and 0 < reach <= BAND_MAX_WINDOW and cache.dtype == torch.bfloat16 and d % 8 == 0 and rank % 8 == 0):
+        banded = [(it.first_token, it.end - it.start, it.start) for it in items if it.end - it.start >= BAND_MIN_TOKENS]
     at = 0
-    for first, n in banded + [(t, 0)]:   # the tokens between the banded portions: runs for the kernel that walks the keys
+    for first, n, _ in banded + [(t, 0, 0)]:   # the tokens between the banded portions: runs for the kernel that walks the keys
         if first > at:
             _latent_attention_walk(q_lat[at:first], cache, table, positions[at:first], token_item[at:first],
                                    None if gate is None else gate[at:first], out[at:first], rank, page_size, window, scale,
@@ -638,10 +642,12 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tens
         lo_t, hi_t = banded[0][0], banded[-1][0] + banded[-1][1]
         check(lib().psb_split_pairs(q_lat[lo_t:hi_t].data_ptr(), q16[lo_t:hi_t].data_ptr(), None,
                                     (hi_t - lo_t) * heads * d, _stream()), "split_pairs")
-        for first, n in banded:
+        for first, n, start in banded:
             for c0 in range(first, first + n, BAND_CHUNK):
-                _latent_attention_band(q16, cache, table, positions, token_item, gate, out, c0, min(BAND_CHUNK, first + n - c0),
-                                       rank, page_size, window, scale)
+                nc = min(BAND_CHUNK, first + n - c0)
+                # no window: the band reaches back to the sequence's first key (the chunk's last position + 1 keys)
+                reach = window or (key_hint if static_shapes else start + (c0 - first) + nc)
+                _latent_attention_band(q16, cache, table, positions, token_item, gate, out, c0, nc, rank, page_size, reach, scale, sink)
     return out
 
 
@@ -670,7 +676,7 @@ def _latent_attention_walk(q_lat, cache, table, positions, token_item, gate, out
           "latent_attention")
 
 
-def _latent_attention_band(q16, cache, table, positions, token_item, gate, out, t0, n, rank, page_size, window, scale) -> None:
+def _latent_attention_band(q16, cache, table, positions, token_item, gate, out, t0, n, rank, page_size, window, scale, sink=None) -> None:
     """Tokens t0 .. t0+n-1 (consecutive tokens of one request) against the window + n - 1 keys they can see."""
     _, heads, d = q16.shape
     kp = -(-(window + n - 1) // 8) * 8
@@ -684,7 +690,7 @@ def _latent_attention_band(q16, cache, table, positions, token_item, gate, out, 
     scores = torch.mm(q16[t0:t0 + n].view(rows, d), band.t(), out_dtype=torch.float32)
     weights = torch.empty((rows, 2 * kp), dtype=torch.bfloat16, device=dev)
     check(lib().psb_latent_band_softmax(scores.data_ptr(), positions.data_ptr(), weights.data_ptr(), t0, n, heads, kp, window,
-                                        float(scale), _stream()), "latent_band_softmax")
+                                        float(scale), _ptr(sink), _stream()), "latent_band_softmax")
     mixed = torch.mm(weights, values2, out_dtype=torch.float32)
     check(lib().psb_latent_band_finish(mixed.data_ptr(), None if gate is None else gate[t0:t0 + n].data_ptr(),
                                        out[t0:t0 + n].data_ptr(), _code(out, "output"), rank, rows * rank, _stream()),
@@ -976,11 +982,15 @@ def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, w_u
         sms = _sms(dev)
         rows = torch.empty((room, h), dtype=torch.bfloat16, device=dev)
         check(lib().psb_moe_gather(x.data_ptr(), row_pair.data_ptr(), rows.data_ptr(), room, h, top, _stream()), "moe_gather")
-        mid = torch.empty((room, ff_in), dtype=torch.bfloat16, device=dev)
-        check(lib().psb_gemm_tcgen05_grouped(rows.data_ptr(), w_up.data_ptr(), mid.data_ptr(), room, ff_in, h, e, tile_expert.data_ptr(),
-                                             MOE_ACTIVATIONS[activation], sms, _stream()), "gemm_tcgen05_grouped")
-        if glu is not None:
-            mid = clipped_glu(mid, *glu)
+        if glu is not None:  # both branches and the gate in one product's epilogue
+            mid = torch.empty((room, ff), dtype=torch.bfloat16, device=dev)
+            check(lib().psb_gemm_tcgen05_grouped_gated_clipped(rows.data_ptr(), w_up.data_ptr(), mid.data_ptr(), room, ff, h, e,
+                                                               tile_expert.data_ptr(), float(glu[0]), float(glu[1]), float(glu[2]),
+                                                               sms, _stream()), "gemm_tcgen05_grouped_gated_clipped")
+        else:
+            mid = torch.empty((room, ff_in), dtype=torch.bfloat16, device=dev)
+            check(lib().psb_gemm_tcgen05_grouped(rows.data_ptr(), w_up.data_ptr(), mid.data_ptr(), room, ff_in, h, e, tile_expert.data_ptr(),
+                                                 MOE_ACTIVATIONS[activation], sms, _stream()), "gemm_tcgen05_grouped")
         y = torch.empty((room, h), dtype=torch.bfloat16, device=dev)
         check(lib().psb_gemm_tcgen05_grouped(mid.data_ptr(), w_down.data_ptr(), y.data_ptr(), room, h, ff, e, tile_expert.data_ptr(),
                                              0, sms, _stream()), "gemm_tcgen05_grouped")

@@ -152,7 +152,7 @@ _SIGNATURES: dict[str, list] = {
     # (x float32, hi, lo, total, stream)
     "psb_split_pairs": [P, P, P, L, P],
     # (scores, positions, weights [rows, 2 KP], t0, n, heads, KP, window, scale, stream)
-    "psb_latent_band_softmax": [P, P, P, I, I, I, I, I, F, P],
+    "psb_latent_band_softmax": [P, P, P, I, I, I, I, I, F, P, P],
     # (o, gate, out, out_dtype, rank, total, stream)
     "psb_latent_band_finish": [P, P, P, I, I, L, P],
     # (proj, dtype, bias_x, conv_w, conv_b, state, positions, token_item, item_start, slots, u_out, T, W, K, num_slots, stream)
@@ -193,6 +193,8 @@ _SIGNATURES: dict[str, list] = {
     "psb_moe_gather": [P, P, P, I, I, I, P],
     # (a, w, c, M, N, K, experts, tile_expert, relu2, sms, stream)
     "psb_gemm_tcgen05_grouped": [P, P, P, I, I, I, I, P, I, I, P],
+    # (a, w, act, M, I, K, experts, tile_expert, limit, alpha, offset, sms, stream)
+    "psb_gemm_tcgen05_grouped_gated_clipped": [P, P, P, I, I, I, I, P, F, F, F, I, P],
     # (a, a_dtype, w, w_dtype, c, c_dtype, offsets, row_pair, pairs, E, N, K, top, gather, act, stream)
     "psb_moe_gemm": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, P],
     # (y, y_dtype, pair_row, weight, shared, shared_dtype, gate, ldg, out, out_dtype, T, H, top, stream)

@@ -140,7 +140,7 @@ class LatentAttention(Mixer):
         mixed = ops.latent_attention(q_lat, cache.kv, table, ctx.positions, ctx.token_item, gate if self.head_gate else None, rank=self.rank,
                                      page_size=cache.page_size, window=self.window, scale=self.scale, out_dtype=x.dtype,
                                      items=ctx.items, key_hint=int(ctx.extras.get("static_kv_len") or ctx.max_kv_len),
-                                     sink=self.sink)
+                                     sink=self.sink, static_shapes=bool(ctx.extras.get("static_kv_len")))
         if self.gate_kind == "channel":  # the values leave their product in float32, meet the gate there, and are rounded once
             values = ops.gate_mul(ops.linear_per_head(mixed, self.w_uv, out_dtype=torch.float32), gate, out_dtype=x.dtype)
         else:
