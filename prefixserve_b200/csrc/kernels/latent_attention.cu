@@ -45,13 +45,12 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, const int32_t*
                                       const float* __restrict__ gain_q, const float* __restrict__ gain_kv,
                                       T* __restrict__ cq_out, float* __restrict__ gate_out, TKV* __restrict__ cache,
                                       int q_rank, int rank, int rot, int rot_dims, int heads, int page_size,
-                                      int num_pages, int max_positions, float eps) {
+                                      int num_pages, int max_positions, float eps, long long ld) {
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
-  const int width = q_rank + rank + rot + heads;
-  const T* row = proj + (size_t)t * width;
+  const T* row = proj + (size_t)t * ld;  // ld >= the row's width: the row may be a run of columns of a wider product
   const int pos = positions[t];
 
   float ss = 0.f;
@@ -99,7 +98,7 @@ template <typename T>
 __global__ void latent_query_rotate_kernel(const T* __restrict__ q, const int32_t* __restrict__ positions,
                                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                            float* __restrict__ q_lat, int heads, int plain, int rot, int rot_dims, int rank,
-                                           int max_positions) {
+                                           int max_positions, long long ldq) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -111,7 +110,7 @@ __global__ void latent_query_rotate_kernel(const T* __restrict__ q, const int32_
   const int per_head = half + (rot - rot_dims);  // work items a head: the pairs, then the elements that pass through
   for (int idx = threadIdx.x; idx < heads * per_head; idx += blockDim.x) {
     const int h = idx / per_head, j = idx - h * per_head;
-    const T* src = q + ((size_t)t * heads + h) * (plain + rot) + plain;
+    const T* src = q + (size_t)t * ldq + (size_t)h * (plain + rot) + plain;  // ldq >= heads * (plain + rot)
     float* dst = q_lat + ((size_t)t * heads + h) * (rank + rot) + rank;
     if (j < half) {
       float o1, o2;
@@ -649,7 +648,8 @@ PSB_API int psb_latent_prepare(const void* proj, int dtype, const void* position
                                int table_width, const void* cos_t, const void* sin_t, const void* gain_q,
                                const void* gain_kv, void* cq_out, void* gate_out, void* cache, int cache_dtype, int T,
                                int q_rank, int rank, int rot, int rot_dims, int heads, int page_size, int num_pages,
-                               int max_positions, float eps, cudaStream_t stream) {
+                               int max_positions, float eps, long long ld, cudaStream_t stream) {
+  if (ld < (long long)q_rank + rank + rot + heads) PSB_REFUSE("latent_prepare: row stride %lld is shorter than the row", ld);
   if (T < 0 || q_rank < 0 || rank < 1 || rot < 0 || heads < 0) PSB_REFUSE("latent_prepare: bad sizes T=%d q_rank=%d rank=%d rot=%d heads=%d", T, q_rank, rank, rot, heads);
   if (rot_dims < 0 || rot_dims > rot || rot_dims % 2) PSB_REFUSE("latent_prepare: %d rotated dimensions must be even and within the rotated part of %d", rot_dims, rot);
   if (rot_dims > 0 && (!cos_t || !sin_t || max_positions < 1)) PSB_REFUSE("latent_prepare: angle tables missing");
@@ -661,7 +661,7 @@ PSB_API int psb_latent_prepare(const void* proj, int dtype, const void* position
       psb_launch(latent_prepare_kernel<T_, TKV>, dim3(T), dim3(q_rank + rank >= 1024 ? 512 : 128), 0, stream, (const T_*)proj, (const int32_t*)positions,
                  (const int32_t*)token_item, (const int32_t*)table, table_width, (const float*)cos_t, (const float*)sin_t,
                  (const float*)gain_q, (const float*)gain_kv, (T_*)cq_out, (float*)gate_out, (TKV*)cache, q_rank, rank, rot,
-                 rot_dims, heads, page_size, num_pages, max_positions, eps);
+                 rot_dims, heads, page_size, num_pages, max_positions, eps, ld);
     });
   });
   PSB_LAUNCH_CHECK("latent_prepare");
@@ -670,14 +670,15 @@ PSB_API int psb_latent_prepare(const void* proj, int dtype, const void* position
 
 PSB_API int psb_latent_query_rotate(const void* q, int dtype, const void* positions, const void* cos_t, const void* sin_t,
                                     void* q_lat, int T, int heads, int plain, int rot, int rot_dims, int rank,
-                                    int max_positions, cudaStream_t stream) {
+                                    int max_positions, long long ldq, cudaStream_t stream) {
   if (T < 0 || heads < 1 || plain < 1 || rot < 0 || rank < 1) PSB_REFUSE("latent_query_rotate: bad sizes");
+  if (ldq < (long long)heads * (plain + rot)) PSB_REFUSE("latent_query_rotate: row stride %lld is shorter than the row", ldq);
   if (rot_dims < 0 || rot_dims > rot || rot_dims % 2) PSB_REFUSE("latent_query_rotate: %d rotated dimensions must be even and within %d", rot_dims, rot);
   if (rot_dims > 0 && (!cos_t || !sin_t || max_positions < 1)) PSB_REFUSE("latent_query_rotate: angle tables missing");
   if (T == 0 || rot == 0) return 0;
   PSB_DISPATCH_DTYPE(dtype, T_, {
     psb_launch(latent_query_rotate_kernel<T_>, dim3(T), dim3(128), 0, stream, (const T_*)q, (const int32_t*)positions,
-               (const float*)cos_t, (const float*)sin_t, (float*)q_lat, heads, plain, rot, rot_dims, rank, max_positions);
+               (const float*)cos_t, (const float*)sin_t, (float*)q_lat, heads, plain, rot, rot_dims, rank, max_positions, ldq);
   });
   PSB_LAUNCH_CHECK("latent_query_rotate");
   return 0;

@@ -542,11 +542,11 @@ def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, token_item: torc
     """One row of the fused projection [query latent | key/value latent | rotated key part | head gates] -> (normed query
     latent [T, q_rank], sigmoid of the gates float32 [T, heads]); the normed key/value latent and the rotated key part
     go to the token's row of the cache [pages, page_size, rank + rot]."""
-    _dev(proj, "projection output"), _dev(cache, "cache entry")
+    _dev(cache, "cache entry")
     _i32(positions, "positions"), _i32(token_item, "token-to-item map"), _i32(table, "page table")
     t = proj.shape[0]
-    if proj.dim() != 2 or proj.shape[1] != q_rank + rank + rot + heads:
-        raise KernelError(f"projection output must be [T, {q_rank + rank + rot + heads}], is {tuple(proj.shape)}")
+    if not proj.is_cuda or proj.dim() != 2 or proj.shape[1] != q_rank + rank + rot + heads or proj.stride(1) != 1:
+        raise KernelError(f"projection output must be [T, {q_rank + rank + rot + heads}] on the device (rows may be part of wider ones), is {tuple(proj.shape)}")
     if cache.numel() % (page_size * (rank + rot)) or cache.shape[-1] != rank + rot or cache.shape[-2] != page_size:
         raise KernelError(f"cache entry must be [pages, .., {page_size}, {rank + rot}], is {tuple(cache.shape)}")
     for what, g, n in (("query latent gain", gain_q, q_rank), ("key/value latent gain", gain_kv, rank)):
@@ -565,7 +565,8 @@ def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, token_item: torc
     check(lib().psb_latent_prepare(proj.data_ptr(), _code(proj, "projection output"), positions.data_ptr(), token_item.data_ptr(),
                                    table.data_ptr(), table.shape[1], _ptr(cos), _ptr(sin), _ptr(gain_q), gain_kv.data_ptr(),
                                    cq.data_ptr(), gate.data_ptr(), cache.data_ptr(), _code(cache, "cache entry"), t, q_rank, rank,
-                                   rot, rot_dims, heads, page_size, cache.shape[0], max_pos, float(eps), _stream()), "latent_prepare")
+                                   rot, rot_dims, heads, page_size, cache.shape[0], max_pos, float(eps), int(proj.stride(0)), _stream()),
+          "latent_prepare")
     return cq, gate
 
 
@@ -573,12 +574,13 @@ def latent_query_rotate(q: torch.Tensor, positions: torch.Tensor, cos: torch.Ten
                         q_lat: torch.Tensor, *, heads: int, plain: int, rot: int, rot_dims: int, rank: int) -> None:
     """q [T, heads * (plain + rot)]: every head's rotated part, turned by the token's position, into q_lat[:, :, rank:]
     (float32 [T, heads, rank + rot])."""
-    _dev(q, "queries"), _dev(q_lat, "latent queries"), _i32(positions, "positions")
+    _dev(q_lat, "latent queries"), _i32(positions, "positions")
     t = q.shape[0]
-    if q.dim() != 2 or q.shape[1] != heads * (plain + rot) or q_lat.dtype != torch.float32 or tuple(q_lat.shape) != (t, heads, rank + rot):
+    if not q.is_cuda or q.dim() != 2 or q.stride(1) != 1 or q.shape[1] != heads * (plain + rot) or q_lat.dtype != torch.float32 or tuple(q_lat.shape) != (t, heads, rank + rot):
         raise KernelError(f"queries {tuple(q.shape)} / latent queries {q_lat.dtype} {tuple(q_lat.shape)} do not fit {heads} heads of {plain}+{rot} and a latent of {rank}")
     check(lib().psb_latent_query_rotate(q.data_ptr(), _code(q, "queries"), positions.data_ptr(), _ptr(cos), _ptr(sin), q_lat.data_ptr(),
-                                        t, heads, plain, rot, rot_dims, rank, cos.shape[0] if cos is not None else 0, _stream()),
+                                        t, heads, plain, rot, rot_dims, rank, cos.shape[0] if cos is not None else 0, int(q.stride(0)),
+                                        _stream()),
           "latent_query_rotate")
 
 

@@ -138,9 +138,9 @@ _SIGNATURES: dict[str, list] = {
     "psb_gate_mul": [P, I, P, P, I, L, P],
     # (proj, dtype, positions, token_item, table, table_width, cos, sin, gain_q, gain_kv, cq_out, gate_out, cache, cache_dtype,
     #  T, q_rank, rank, rot, rot_dims, heads, page_size, num_pages, max_positions, eps, stream)
-    "psb_latent_prepare": [P, I, P, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P],
+    "psb_latent_prepare": [P, I, P, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, L, P],
     # (q, dtype, positions, cos, sin, q_lat, T, heads, plain, rot, rot_dims, rank, max_positions, stream)
-    "psb_latent_query_rotate": [P, I, P, P, P, P, I, I, I, I, I, I, I, P],
+    "psb_latent_query_rotate": [P, I, P, P, P, P, I, I, I, I, I, I, I, L, P],
     # (q_lat, cache, cache_dtype, table, table_width, positions, token_item, gate, out, out_dtype, T, heads, rank, rot,
     #  page_size, num_pages, window, scale, heads_per_block, splits, partial, stream)
     "psb_latent_attention": [P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P],

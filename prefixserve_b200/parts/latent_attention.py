@@ -121,11 +121,12 @@ class LatentAttention(Mixer):
         proj = ops.linear(x, self.w_in)
         gates = heads if self.head_gate else (heads * self.vdim if self.gate_kind == "channel" else 0)
         if self.q_rank is None:
-            # the row is [queries | key/value latent | rotated key part | gates]: the queries are copied out, the rest
-            # goes through the pass that norms, rotates, appends and takes the gates' sigmoids
+            # the row is [queries | key/value latent | rotated key part | gates]: the queries are read where they lie, the
+            # rest goes through the pass that norms, rotates, appends and takes the gates' sigmoids (both kernels, and the
+            # per-head product, take rows that are runs of columns of a wider product)
             qw = heads * (self.dim + self.rot)
-            q = proj[:, :qw].contiguous()
-            _, gate = ops.latent_prepare(proj[:, qw:].contiguous(), ctx.positions, ctx.token_item, table, self.position.cos,
+            q = proj[:, :qw]
+            _, gate = ops.latent_prepare(proj[:, qw:], ctx.positions, ctx.token_item, table, self.position.cos,
                                          self.position.sin, None, self.gain_kv, cache.kv, q_rank=0, rank=self.rank, rot=self.rot,
                                          rot_dims=self.rot_dims, heads=gates, page_size=cache.page_size, eps=self.eps)
         else:
