@@ -22,6 +22,11 @@
 // expert than the rows alone would need, whatever the routing turns out to be, so its shape does not depend on it).
 // ``gather``: A's row is the pair's token (first product) or the row itself (second).  act: none or relu squared.
 //
+// ``glu`` (second product of gated experts): A holds, per row, K gate values followed by K up values as the first
+// product left them, and the operand is g * sigmoid(alpha g) * (u + offset) with g = min(gate, limit), u = clamp(up,
+// -limit, limit), taken in float32 as the row is read and rounded to A's type: the gate costs no pass of its own, and a
+// row that belongs to nobody is never read.
+//
 // moe_mma_kernel: the same product for bfloat16 operands on the tensor cores (mma.sync m16n8k16, float32 sums).
 // moe_fewrows_kernel: the same for steps with no more than four rows an expert on average (see there).
 //
@@ -200,6 +205,20 @@ __device__ __forceinline__ float moe_act(float v, int act) {
   return v;
 }
 
+// eight gated values from eight gate and eight up values (bfloat16), rounded to bfloat16
+__device__ __forceinline__ uint4 glu8(const uint4& g4, const uint4& u4, const GluClip& c) {
+  const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+  const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+  uint4 o4;
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+    o2[k] = __floats2bfloat162_rn(clipped_gate_value(g.x, u.x, c), clipped_gate_value(g.y, u.y, c));
+  }
+  return o4;
+}
+
 constexpr int TILE = 64;
 constexpr int BK = 16;
 constexpr int THREADS = 256;
@@ -207,7 +226,8 @@ constexpr int THREADS = 256;
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(THREADS)
 moe_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C, const int32_t* __restrict__ offsets,
-                const int32_t* __restrict__ row_pair, int E, int N, int K, int top, int gather, int act) {
+                const int32_t* __restrict__ row_pair, int E, int N, int K, int top, int gather, int act, int glu,
+                const GluClip clip) {
   __shared__ float sa[BK][TILE + 4];
   __shared__ float sw[BK][TILE + 4];
   __shared__ int src[TILE];
@@ -232,7 +252,16 @@ moe_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restri
     for (int j = 0; j < 4; ++j) {
       const int k = k0 + lcol + j;
       const int n = n0 + lrow;
-      sa[lcol + j][lrow] = (arow >= 0 && k < K) ? to_float<TA>(A[(size_t)arow * K + k]) : 0.f;
+      float av = 0.f;
+      if (arow >= 0 && k < K) {
+        if (glu) {
+          const TA* ar = A + (size_t)arow * 2 * K;
+          av = to_float<TA>(from_float<TA>(clipped_gate_value(to_float<TA>(ar[k]), to_float<TA>(ar[K + k]), clip)));
+        } else {
+          av = to_float<TA>(A[(size_t)arow * K + k]);
+        }
+      }
+      sa[lcol + j][lrow] = av;
       sw[lcol + j][lrow] = (n < N && k < K) ? to_float<TW>(W[(size_t)n * K + k]) : 0.f;
     }
     __syncthreads();
@@ -277,7 +306,7 @@ template <typename TC>
 __global__ void __launch_bounds__(128)
 moe_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, TC* __restrict__ C,
                const int32_t* __restrict__ offsets, const int32_t* __restrict__ row_pair, int E, int N, int K, int top,
-               int gather, int act) {
+               int gather, int act, int glu, const GluClip clip) {
   __shared__ __align__(16) __nv_bfloat16 sa[TILE][BKM + 8];
   __shared__ __align__(16) __nv_bfloat16 sw[TILE][BKM + 8];
   __shared__ int src[TILE];
@@ -304,7 +333,14 @@ moe_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restr
       const int r = piece >> 2, c = (piece & 3) * 8;
       uint4 va = make_uint4(0, 0, 0, 0), vw = make_uint4(0, 0, 0, 0);
       if (k0 + c < K) {
-        if (src[r] >= 0) va = *reinterpret_cast<const uint4*>(A + (size_t)src[r] * K + k0 + c);
+        if (src[r] >= 0) {
+          if (glu) {
+            const __nv_bfloat16* ar = A + (size_t)src[r] * 2 * K + k0 + c;
+            va = glu8(*reinterpret_cast<const uint4*>(ar), *reinterpret_cast<const uint4*>(ar + K), clip);
+          } else {
+            va = *reinterpret_cast<const uint4*>(A + (size_t)src[r] * K + k0 + c);
+          }
+        }
         if (n0 + r < N) vw = *reinterpret_cast<const uint4*>(W + (size_t)(n0 + r) * K + k0 + c);
       }
       *reinterpret_cast<uint4*>(&sa[r][c]) = va;
@@ -353,7 +389,7 @@ template <typename TC>
 __global__ void __launch_bounds__(FEW_WARPS * 32, 3)
 moe_fewrows_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, TC* __restrict__ C,
                    const int32_t* __restrict__ offsets, const int32_t* __restrict__ row_pair, int N, int K, int top, int gather,
-                   int act) {
+                   int act, int glu, const GluClip clip) {
   extern __shared__ __align__(16) unsigned char few_smem[];
   __nv_bfloat16* rows = reinterpret_cast<__nv_bfloat16*>(few_smem);  // [FEW_ROWS][K]
   pdl_trigger();
@@ -371,7 +407,14 @@ moe_fewrows_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
       if (r < m) {
         const int pair = row_pair[r0 + r];
         const int src = pair < 0 ? -1 : (gather ? pair / top : r0 + r);
-        if (src >= 0) v = reinterpret_cast<const uint4*>(A + (size_t)src * K)[c];
+        if (src >= 0) {
+          if (glu) {
+            const uint4* ar = reinterpret_cast<const uint4*>(A + (size_t)src * 2 * K);
+            v = glu8(ar[c], ar[K / 8 + c], clip);
+          } else {
+            v = reinterpret_cast<const uint4*>(A + (size_t)src * K)[c];
+          }
+        }
       }
       reinterpret_cast<uint4*>(rows)[i] = v;
     }
@@ -487,10 +530,14 @@ PSB_API int psb_moe_gather(const void* x, const void* row_pair, void* out, int r
 }
 
 // ``pairs``: the rows the layout has room for (every expert may have one partly filled tile more than its rows need).
-// (a, a_dtype, w, w_dtype, c, c_dtype, offsets, row_pair, pairs, E, N, K, top, gather, act, stream)
+// ``glu`` 1 (with gather 0): a's rows are [gate (K) | up (K)] and the clipped gate (limit, alpha, offset) is taken as they are read.
+// (a, a_dtype, w, w_dtype, c, c_dtype, offsets, row_pair, pairs, E, N, K, top, gather, act, glu, limit, alpha, offset, stream)
 PSB_API int psb_moe_gemm(const void* a, int a_dtype, const void* w, int w_dtype, void* c, int c_dtype, const void* offsets,
-                         const void* row_pair, int pairs, int E, int N, int K, int top, int gather, int act, cudaStream_t stream) {
+                         const void* row_pair, int pairs, int E, int N, int K, int top, int gather, int act, int glu, float limit,
+                         float alpha, float offset, cudaStream_t stream) {
   if (pairs < 0 || E < 1 || E > MAX_EXPERTS || N < 1 || K < 1 || top < 1) PSB_REFUSE("moe_gemm: bad sizes");
+  if (glu && (gather || !(limit > 0.f))) PSB_REFUSE("moe_gemm: the gate on the rows goes with the second product and a positive limit");
+  const GluClip clip{limit, alpha, offset};
   if (act != MOE_ACT_NONE && act != MOE_ACT_RELU2) PSB_REFUSE("moe_gemm: activation code %d is not built", act);
   if (pairs == 0) return 0;
   const long long row_tiles = (pairs + TILE - 1) / TILE + E;
@@ -510,7 +557,7 @@ PSB_API int psb_moe_gemm(const void* a, int a_dtype, const void* w, int w_dtype,
         done.set();
       }
       psb_launch(kernel, few_grid, dim3(FEW_WARPS * 32), few_smem, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (TC*)c,
-                 (const int32_t*)offsets, (const int32_t*)row_pair, N, K, top, gather, act);
+                 (const int32_t*)offsets, (const int32_t*)row_pair, N, K, top, gather, act, glu, clip);
     });
     PSB_LAUNCH_CHECK("moe_gemm");
     return 0;
@@ -518,7 +565,7 @@ PSB_API int psb_moe_gemm(const void* a, int a_dtype, const void* w, int w_dtype,
   if (a_dtype == PSB_BF16 && w_dtype == PSB_BF16 && K % 8 == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0) {
     PSB_DISPATCH_DTYPE(c_dtype, TC, {
       psb_launch(moe_mma_kernel<TC>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (TC*)c,
-                 (const int32_t*)offsets, (const int32_t*)row_pair, E, N, K, top, gather, act);
+                 (const int32_t*)offsets, (const int32_t*)row_pair, E, N, K, top, gather, act, glu, clip);
     });
     PSB_LAUNCH_CHECK("moe_gemm");
     return 0;
@@ -527,7 +574,7 @@ PSB_API int psb_moe_gemm(const void* a, int a_dtype, const void* w, int w_dtype,
     PSB_DISPATCH_DTYPE(w_dtype, TW, {
       PSB_DISPATCH_DTYPE(c_dtype, TC, {
         psb_launch(moe_gemm_kernel<TA, TW, TC>, grid, dim3(THREADS), 0, stream, (const TA*)a, (const TW*)w, (TC*)c,
-                   (const int32_t*)offsets, (const int32_t*)row_pair, E, N, K, top, gather, act);
+                   (const int32_t*)offsets, (const int32_t*)row_pair, E, N, K, top, gather, act, glu, clip);
       });
     });
   });

@@ -998,16 +998,15 @@ def moe_experts(x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, w_u
                                              0, sms, _stream()), "gemm_tcgen05_grouped")
     else:
         mid = torch.empty((room, ff_in), dtype=x.dtype, device=dev)
-        if glu is not None:
-            mid.zero_()  # rows that belong to nobody are not written by the product, and the gate reads every row
         check(lib().psb_moe_gemm(x.data_ptr(), _code(x, "expert input"), w_up.data_ptr(), _code(w_up, "expert up matrices"), mid.data_ptr(),
                                  _code(mid, "expert activations"), offsets.data_ptr(), row_pair.data_ptr(), room, e, ff_in, h, top, 1,
-                                 MOE_ACTIVATIONS[activation], _stream()), "moe_gemm")
-        if glu is not None:
-            mid = clipped_glu(mid, *glu)
+                                 MOE_ACTIVATIONS[activation], 0, 0.0, 0.0, 0.0, _stream()), "moe_gemm")
+        # gated experts: the second product takes the clipped gate of a row's two halves as it reads the row
+        lim, alpha, off = (float(v) for v in glu) if glu is not None else (0.0, 0.0, 0.0)
         y = torch.empty((room, h), dtype=torch.float32, device=dev)
         check(lib().psb_moe_gemm(mid.data_ptr(), _code(mid, "expert activations"), w_down.data_ptr(), _code(w_down, "expert down matrices"),
-                                 y.data_ptr(), F32, offsets.data_ptr(), row_pair.data_ptr(), room, e, h, ff, top, 0, 0, _stream()), "moe_gemm")
+                                 y.data_ptr(), F32, offsets.data_ptr(), row_pair.data_ptr(), room, e, h, ff, top, 0, 0,
+                                 1 if glu is not None else 0, lim, alpha, off, _stream()), "moe_gemm")
     out = torch.empty((t, h), dtype=out_dtype or x.dtype, device=dev)
     ldg = 0
     if shared is not None:

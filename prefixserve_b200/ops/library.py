@@ -196,7 +196,7 @@ _SIGNATURES: dict[str, list] = {
     # (a, w, act, M, I, K, experts, tile_expert, limit, alpha, offset, sms, stream)
     "psb_gemm_tcgen05_grouped_gated_clipped": [P, P, P, I, I, I, I, P, F, F, F, I, P],
     # (a, a_dtype, w, w_dtype, c, c_dtype, offsets, row_pair, pairs, E, N, K, top, gather, act, stream)
-    "psb_moe_gemm": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, P],
+    "psb_moe_gemm": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, I, F, F, F, P],
     # (y, y_dtype, pair_row, weight, shared, shared_dtype, gate, ldg, out, out_dtype, T, H, top, stream)
     "psb_moe_combine": [P, I, P, P, P, I, P, I, P, I, I, I, I, P],
     # (x, dtype, mix, state, stride, positions, token_item, item_start, slots, y, T, W, num_slots, stream)
