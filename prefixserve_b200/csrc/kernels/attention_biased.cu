@@ -108,7 +108,8 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
                         int table_width, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_item,
                         const float* __restrict__ bias, const float* __restrict__ sink, T* __restrict__ out, int T_tokens,
                         int hq, int hkv, int dim, int vdim, int page_size, int window, int chunk, int reach, float scale,
-                        const int32_t* __restrict__ item_start, int skip_from, int keep_first) {
+                        const int32_t* __restrict__ item_start, int skip_from, int keep_first, float* __restrict__ partial,
+                        int splits) {
   __shared__ __align__(16) float qs[MAX_D];
   __shared__ float part[WARPS][MAX_D + 2];
   pdl_trigger();
@@ -118,6 +119,9 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
   const int g = h / (hq / hkv);
   const int p = positions[t];
   const int item = token_item[t];
+  // ``splits`` > 1 (steps of few tokens over many keys): blockIdx.y names this block's share of the runs; it leaves its
+  // maximum, sum and unnormalised output in ``partial`` [T * hq, splits, vdim + 2] and the merge kernel joins the shares
+  const int split = blockIdx.y;
   if (skip_from > 0 && item_start[item + 1] - item_start[item] >= skip_from) return;  // the tiled kernel's token
   const int32_t* pages = table + (size_t)item * table_width;
   const T* qrow = q + ((size_t)t * hq + h) * dim;
@@ -145,7 +149,7 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
 #pragma unroll
   for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
 
-  for (int run = warp;; run += WARPS) {
+  for (int run = warp + WARPS * split;; run += WARPS * splits) {
     const bool kept = run < kept_runs;
     const int base = kept ? 32 * run : (lo & ~31) + 32 * (run - kept_runs);
     if (base > p) break;
@@ -197,8 +201,9 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
   if (lane == 0) { part[warp][MAX_D] = m; part[warp][MAX_D + 1] = l; }
   __syncthreads();
   if (warp != 0) return;
-  // join: the sink first (maximum = sink, sum = 1, no value), then the warps in order
-  float M = sink ? sink[h] : -FLT_MAX, L = sink ? 1.f : 0.f;
+  // join: the sink first (maximum = sink, sum = 1, no value; with split keys it joins in the merge kernel), then the warps in order
+  const bool sink_here = sink && splits == 1;
+  float M = sink_here ? sink[h] : -FLT_MAX, L = sink_here ? 1.f : 0.f;
 #pragma unroll
   for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
   for (int w = 0; w < WARPS; ++w) {
@@ -214,8 +219,57 @@ attention_biased_kernel(const T* __restrict__ q, const TKV* __restrict__ kv, con
     }
     M = m_new;
   }
+  if (splits > 1) {
+    float* mine = partial + (((size_t)t * hq + h) * splits + split) * (vdim + 2);
+    if (lane == 0) { mine[0] = M; mine[1] = L; }
+#pragma unroll
+    for (int i = 0; i < MAX_D / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < vdim) mine[2 + d] = acc[i];
+    }
+    return;
+  }
   const float inv = 1.f / L;
   T* orow = out + ((size_t)t * hq + h) * vdim;
+#pragma unroll
+  for (int i = 0; i < MAX_D / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < vdim) orow[d] = from_float<T>(acc[i] * inv);
+  }
+}
+
+// Joins the shares of the blocks that split a (token, head)'s runs among them, in split order, the sink first.
+constexpr int MAX_KEY_SPLITS = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(32)
+attention_biased_merge_kernel(const float* __restrict__ partial, const float* __restrict__ sink, T* __restrict__ out, int hq,
+                              int vdim, int splits) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t unit = blockIdx.x;  // token * hq + head
+  const int lane = threadIdx.x, h = (int)(unit % hq);
+  const float* mine = partial + unit * splits * (vdim + 2);
+  float M = sink ? sink[h] : -FLT_MAX, L = sink ? 1.f : 0.f;
+  float acc[MAX_D / 32];
+#pragma unroll
+  for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* share = mine + (size_t)s * (vdim + 2);
+    const float ms = share[0], ls = share[1];
+    if (ls == 0.f) continue;  // a share without keys
+    const float m_new = fmaxf(M, ms);
+    const float a = expf(M - m_new), b2 = expf(ms - m_new);
+    L = L * a + ls * b2;
+#pragma unroll
+    for (int i = 0; i < MAX_D / 32; ++i) {
+      const int d = lane + 32 * i;
+      if (d < vdim) acc[i] = acc[i] * a + share[2 + d] * b2;
+    }
+    M = m_new;
+  }
+  const float inv = 1.f / L;
+  T* orow = out + unit * vdim;
 #pragma unroll
   for (int i = 0; i < MAX_D / 32; ++i) {
     const int d = lane + 32 * i;
@@ -624,11 +678,14 @@ PSB_API int psb_attention_biased_append(const void* qkv, int dtype, const void* 
 
 // ``skip_from`` > 0: tokens of portions with at least that many tokens are left to the tiled kernel (item_start needed).
 // (q, dtype, kv, kv_dtype, table, table_width, positions, token_item, bias, sink, out, T, hq, hkv, dim, vdim, page_size,
-//  window, chunk, reach, scale, item_start, skip_from, keep_first, stream)
+//  window, chunk, reach, scale, item_start, skip_from, keep_first, partial [T * hq, splits, vdim + 2] float32 or null, splits, stream)
 PSB_API int psb_attention_biased(const void* q, int dtype, const void* kv, int kv_dtype, const void* table, int table_width,
                                  const void* positions, const void* token_item, const void* bias, const void* sink, void* out,
                                  int T, int hq, int hkv, int dim, int vdim, int page_size, int window, int chunk, int reach,
-                                 float scale, const void* item_start, int skip_from, int keep_first, cudaStream_t stream) {
+                                 float scale, const void* item_start, int skip_from, int keep_first, void* partial, int splits,
+                                 cudaStream_t stream) {
+  if (splits < 1 || splits > MAX_KEY_SPLITS || (splits > 1 && (!partial || skip_from > 0)))
+    PSB_REFUSE("attention_biased: 1 to %d shares of the keys (with their scratch, and no tokens left to another kernel), not %d", MAX_KEY_SPLITS, splits);
   if (keep_first < 0 || (keep_first > 0 && (window < 1 || chunk > 0))) PSB_REFUSE("attention_biased: kept first keys go with a window and no chunk mask");
   if (skip_from > 0 && !item_start) PSB_REFUSE("attention_biased: skipping tiled portions needs the item offsets");
   if (T < 0 || hq < 1 || hkv < 1 || hq % hkv) PSB_REFUSE("attention_biased: %d query heads cannot share %d key/value heads", hq, hkv);
@@ -640,13 +697,20 @@ PSB_API int psb_attention_biased(const void* q, int dtype, const void* kv, int k
   if (blocks > 0x7fffffffLL) PSB_REFUSE("attention_biased: batch too large");
   PSB_DISPATCH_DTYPE(dtype, T_, {
     PSB_DISPATCH_DTYPE(kv_dtype, TKV, {
-      psb_launch(attention_biased_kernel<T_, TKV>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, (const T_*)q,
+      psb_launch(attention_biased_kernel<T_, TKV>, dim3((unsigned)blocks, (unsigned)splits), dim3(WARPS * 32), 0, stream, (const T_*)q,
                  (const TKV*)kv, (const int32_t*)table, table_width, (const int32_t*)positions, (const int32_t*)token_item,
                  (const float*)bias, (const float*)sink, (T_*)out, T, hq, hkv, dim, vdim, page_size, window, chunk, reach, scale,
-                 (const int32_t*)item_start, skip_from, keep_first);
+                 (const int32_t*)item_start, skip_from, keep_first, (float*)partial, splits);
     });
   });
   PSB_LAUNCH_CHECK("attention_biased");
+  if (splits > 1) {
+    PSB_DISPATCH_DTYPE(dtype, T_, {
+      psb_launch(attention_biased_merge_kernel<T_>, dim3((unsigned)blocks), dim3(32), 0, stream, (const float*)partial,
+                 (const float*)sink, (T_*)out, hq, vdim, splits);
+    });
+    PSB_LAUNCH_CHECK("attention_biased_merge");
+  }
   return 0;
 }
 

@@ -796,6 +796,11 @@ BIASED_MMA = True            # ... the tensor-core one where the sizes allow (mu
 # The tensor-core kernel also takes single tokens and short portions: its blocks bring keys and values in with wide,
 # coalesced loads of all threads, which is what a decode step is bound by (the rows of its tile that have no token idle).
 BIASED_MMA_MIN_TOKENS = 1
+# Steps in which every item is a single token: the kernel that walks the keys, with the runs of a (token, head) shared out
+# among up to 16 blocks and a merge kernel behind them (a step of 8 tokens is 128 blocks of one warp's work each otherwise,
+# every one of them a chain of a thousand keys).  BIASED_BLOCKS_WANTED blocks keep every SM busy; no share below 128 keys.
+BIASED_SPLIT_DECODE = True
+BIASED_BLOCKS_WANTED = 2368
 
 
 def biased_attention(qkv: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,
@@ -853,6 +858,21 @@ def attention_over_rows(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, 
     # the launches have the same shape whatever the step holds).
     item_start = _i32(ctx.item_start, "item offsets")
     both16 = q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16
+    if BIASED_SPLIT_DECODE and ctx.max_new_tokens == 1:
+        extras = getattr(ctx, "extras", None) or {}
+        keys = int(extras.get("static_kv_len") or ctx.max_kv_len)  # a captured step is sized for its class of lengths
+        if win:
+            keys = min(keys, win + keep_first)
+        if chk:
+            keys = min(keys, chk)
+        splits = max(1, min(16, -(-BIASED_BLOCKS_WANTED // max(t * num_heads, 1)), keys // 128))
+        partial = torch.empty((t, num_heads, splits, vdim + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
+        check(lib().psb_attention_biased(q.data_ptr(), _code(q, "queries"), kv.data_ptr(), _code(kv, "cache entry"),
+                                         table.data_ptr(), table.shape[1], positions.data_ptr(), token_item.data_ptr(),
+                                         _ptr(bias), _ptr(sink), out.data_ptr(), t, num_heads, num_kv_heads, dim, vdim,
+                                         page_size, win, chk, reach, float(scale), item_start.data_ptr(), 0, keep_first,
+                                         _ptr(partial), splits, _stream()), "attention_biased")
+        return out
     on_tensor_cores = both16 and BIASED_MMA and bool(lib().psb_attention_biased_mma_supported(num_heads, num_kv_heads, dim, vdim))
     least = BIASED_MMA_MIN_TOKENS if on_tensor_cores else BIASED_TILE_MIN_TOKENS
     long_portions = both16 and ctx.max_new_tokens >= least
@@ -862,7 +882,7 @@ def attention_over_rows(q: torch.Tensor, kv: torch.Tensor, table: torch.Tensor, 
                                          table.data_ptr(), table.shape[1], positions.data_ptr(), token_item.data_ptr(),
                                          _ptr(bias), _ptr(sink), out.data_ptr(), t, num_heads, num_kv_heads, dim, vdim,
                                          page_size, win, chk, reach, float(scale), item_start.data_ptr(),
-                                         least if tiled else 0, keep_first, _stream()), "attention_biased")
+                                         least if tiled else 0, keep_first, None, 1, _stream()), "attention_biased")
     if tiled:
         entry = lib().psb_attention_biased_mma if on_tensor_cores else lib().psb_attention_biased_tiles
         check(entry(q.data_ptr(), kv.data_ptr(), table.data_ptr(), table.shape[1], positions.data_ptr(), item_start.data_ptr(),

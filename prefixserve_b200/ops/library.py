@@ -169,7 +169,7 @@ _SIGNATURES: dict[str, list] = {
     "psb_attention_biased_append": [P, I, P, P, P, I, P, I, P, I, I, I, I, I, I, I, P],
     # (q, dtype, kv, kv_dtype, table, table_width, positions, token_item, bias, sink, out, T, hq, hkv, dim, vdim, page_size,
     #  window, chunk, reach, scale, item_start, skip_from, stream)
-    "psb_attention_biased": [P, I, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, I, I, P],
+    "psb_attention_biased": [P, I, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, I, I, P, I, P],
     "psb_attention_biased_tile_tokens": [],
     "psb_attention_biased_tile_supported": [I, I, I, I],
     # (q, kv, table, table_width, positions, item_start, items, T, min_tokens, bias, sink, out, hq, hkv, dim, vdim,
