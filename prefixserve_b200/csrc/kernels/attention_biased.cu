@@ -250,23 +250,33 @@ attention_biased_merge_kernel(const float* __restrict__ partial, const float* __
   const size_t unit = blockIdx.x;  // token * hq + head
   const int lane = threadIdx.x, h = (int)(unit % hq);
   const float* mine = partial + unit * splits * (vdim + 2);
-  float M = sink ? sink[h] : -FLT_MAX, L = sink ? 1.f : 0.f;
+  // every share's maximum and sum are asked for at once, then every share's output: nothing here waits for a share before
+  // it asks for the next
+  float ms[MAX_KEY_SPLITS], ls[MAX_KEY_SPLITS];
+#pragma unroll
+  for (int s = 0; s < MAX_KEY_SPLITS; ++s) {
+    ms[s] = s < splits ? mine[(size_t)s * (vdim + 2)] : -FLT_MAX;
+    ls[s] = s < splits ? mine[(size_t)s * (vdim + 2) + 1] : 0.f;
+  }
+  float M = sink ? sink[h] : -FLT_MAX;
+#pragma unroll
+  for (int s = 0; s < MAX_KEY_SPLITS; ++s)
+    if (ls[s] > 0.f) M = fmaxf(M, ms[s]);  // (a share without keys has a sum of zero)
+  float L = sink ? expf(sink[h] - M) : 0.f;
   float acc[MAX_D / 32];
 #pragma unroll
   for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float* share = mine + (size_t)s * (vdim + 2);
-    const float ms = share[0], ls = share[1];
-    if (ls == 0.f) continue;  // a share without keys
-    const float m_new = fmaxf(M, ms);
-    const float a = expf(M - m_new), b2 = expf(ms - m_new);
-    L = L * a + ls * b2;
+#pragma unroll
+  for (int s = 0; s < MAX_KEY_SPLITS; ++s) {
+    if (s >= splits) break;
+    const float f = ls[s] > 0.f ? expf(ms[s] - M) : 0.f;
+    L += ls[s] * f;
+    const float* share = mine + (size_t)s * (vdim + 2) + 2;
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) {
       const int d = lane + 32 * i;
-      if (d < vdim) acc[i] = acc[i] * a + share[2 + d] * b2;
+      if (d < vdim) acc[i] = fmaf(share[d], f, acc[i]);
     }
-    M = m_new;
   }
   const float inv = 1.f / L;
   T* orow = out + unit * vdim;
