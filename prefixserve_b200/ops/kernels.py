@@ -653,8 +653,24 @@ def latent_attention(q_lat: torch.Tensor, cache: torch.Tensor, table: torch.Tens
     return out
 
 
-ROWS_BLOCKS_WANTED = 296   # blocks that keep every SM of a B200 busy with the kernel that reads rows side by side (two an SM)
+# The kernel that reads rows side by side holds a (token, head pair)'s sums in registers (234 a thread with two heads): one
+# block of eight warps an SM.  Its blocks walk their keys in a chain of dependent loads, so a launch costs (rounds of blocks
+# over the SMs) x (keys a block + a fixed share); the keys of a (token, heads) are split among as many blocks as makes that
+# least (8 tokens of 16 heads over 2,048 keys: 64 units x 2 blocks in one round, 1,024 keys each, instead of 64 x 5 in three
+# rounds of 410: 105 -> 86 us a layer).
+ROWS_BLOCK_SHARE = 96      # what a block costs beyond its keys, in keys
 ROWS_KEYS_PER_SPLIT = 128  # no block of that kernel is given fewer keys than this by splitting
+
+
+def _rows_splits(blocks: int, keys: int, slots: int) -> int:
+    best, best_cost = 1, None
+    for s in range(1, 9):
+        if s > 1 and keys // s < ROWS_KEYS_PER_SPLIT:
+            break
+        cost = -(-blocks * s // slots) * (keys / s + ROWS_BLOCK_SHARE)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def _latent_attention_walk(q_lat, cache, table, positions, token_item, gate, out, rank, page_size, window, scale,
@@ -667,8 +683,9 @@ def _latent_attention_walk(q_lat, cache, table, positions, token_item, gate, out
         if heads % 2 == 0 and d <= 768:
             hp = 2  # two heads of a token share a block and every row it loads
         blocks = t * heads // hp
-        if blocks < ROWS_BLOCKS_WANTED and key_hint >= 2 * ROWS_KEYS_PER_SPLIT:
-            splits = max(1, min(8, -(-ROWS_BLOCKS_WANTED // blocks), key_hint // ROWS_KEYS_PER_SPLIT))
+        if key_hint >= 2 * ROWS_KEYS_PER_SPLIT:
+            from .tensorcore import _sms
+            splits = _rows_splits(blocks, key_hint, _sms(q_lat.device))
         if splits > 1:
             partial = torch.empty((t, heads, splits, rank + 2), dtype=torch.float32, device=q_lat.device)
     check(lib().psb_latent_attention(q_lat.data_ptr(), cache.data_ptr(), _code(cache, "cache entry"), table.data_ptr(), table.shape[1],
